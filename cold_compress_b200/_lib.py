@@ -134,7 +134,7 @@ def check(rc: int, what: str = "") -> int:
 
 # --------------------------------------------------------------------------- libcc_b200_seq.so (include/cc_b200_seq.h)
 SEQ_SO_PATH = Path(os.environ.get("CC_B200_SEQ_LIB", PKG / "libcc_b200_seq.so"))
-SEQ_ABI_VERSION = 2
+SEQ_ABI_VERSION = 3
 DT_F32, DT_BF16 = 0, 1
 SINK_NONE, SINK_LEARNED, SINK_ZERO = 0, 1, 2
 
@@ -143,7 +143,8 @@ class CcSeqAttn(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("q", "k_new", "v_new", "k_cache", "v_cache", "pos", "mask", "cache_cts",
                                           "input_pos", "y", "sink")] + [
         (n, C.c_int32) for n in ("T", "H", "G", "Dk", "Dv", "L", "window", "sink_mode", "cache_dtype", "y_dtype")] + [
-        ("scale", C.c_float), ("append", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64)]
+        ("scale", C.c_float), ("append", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
+        ("block", C.c_int32)]
 
 
 class CcSeqGemv(C.Structure):
@@ -171,7 +172,7 @@ SEQ_EXPORTS = {
 }
 
 # ---- second part of the header: state-carrying layers (csrc/seq/mix_kernels.cu)
-ACT_NONE, ACT_GELU_TANH, ACT_SILU, ACT_TANH, ACT_SIGMOID = range(5)
+ACT_NONE, ACT_GELU_TANH, ACT_SILU, ACT_TANH, ACT_SIGMOID, ACT_RELU_SQ = range(6)
 _i64 = C.c_int64
 
 
@@ -240,6 +241,43 @@ SEQ_EXPORTS.update({
     "cc_seq_gather_rows": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "cc_seq_moe_expert_tokens": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "cc_seq_moe_combine": (C.c_int, [C.POINTER(CcSeqMoeCombine), _vp]),
+})
+
+# ---- third part of the header: post-sum norms, short convolutions, matrix-state scans, rotations (csrc/seq/scan_kernels.cu)
+class CcSeqSumNorm(C.Structure):
+    _fields_ = [("x", _vp), ("y", _vp), ("ldy", _i64), ("y_norm_w", _vp), ("y2", _vp), ("ldy2", _i64), ("y2_norm_w", _vp),
+                ("y_coef", _f32), ("y_scale", _vp), ("w", _vp), ("alpha", _f32), ("eps", _f32), ("gain_offset", _f32),
+                ("center", _i32), ("out", _vp), ("stack", _vp), ("stack_stride", _i64), ("n_prev", _i32), ("coef", _vp),
+                ("mix", _vp), ("out_act", _vp), ("act_dtype", _i32), ("rows", _vp), ("T", _i32), ("E", _i32)]
+
+
+class CcSeqSsdScan(C.Structure):
+    _fields_ = [("x", _vp), ("ldx", _i64), ("B", _vp), ("C", _vp), ("ldbc", _i64), ("dt_raw", _vp), ("lddt", _i64),
+                ("dt_bias", _vp), ("A_log", _vp), ("D", _vp), ("state", _vp), ("y", _vp)] + [
+        (n, _i32) for n in ("T", "H", "G", "N", "V")]
+
+
+class CcSeqDeltaScan(C.Structure):
+    _fields_ = [("q", _vp), ("k", _vp), ("ldqk", _i64), ("v", _vp), ("ldv", _i64), ("beta_raw", _vp), ("ldb", _i64),
+                ("a_raw", _vp), ("lda", _i64), ("dt_bias", _vp), ("A_log", _vp), ("state", _vp), ("o", _vp)] + [
+        (n, _i32) for n in ("T", "H", "G", "D", "V")] + [("q_scale", _f32), ("unit_eps", _f32)]
+
+
+class CcSeqQkvRope(C.Structure):
+    _fields_ = [("inp", _vp), ("ld", _i64)] + [(n, _i32) for n in ("off_q", "off_k", "off_v", "H", "G", "Dk", "Dv")] + [
+        ("q_norm_w", _vp), ("k_norm_w", _vp), ("eps", _f32), ("rot_dims", _i32), ("interleaved", _i32), ("inv_freq", _vp),
+        ("v_inv_freq", _vp), ("input_pos", _vp), ("q_out", _vp), ("k_out", _vp), ("v_out", _vp), ("out_dtype", _i32), ("T", _i32)]
+
+
+SEQ_EXPORTS.update({
+    "cc_seq_sum_norm": (C.c_int, [C.POINTER(CcSeqSumNorm), _vp]),
+    "cc_seq_short_conv": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp]),
+    "cc_seq_ssd_scan": (C.c_int, [C.POINTER(CcSeqSsdScan), _vp]),
+    "cc_seq_delta_scan": (C.c_int, [C.POINTER(CcSeqDeltaScan), _vp]),
+    "cc_seq_gated_rms_groups": (C.c_int, [_vp, _vp, _i64, _i32, _i32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _f32, _vp]),
+    "cc_seq_qkv_rope": (C.c_int, [C.POINTER(CcSeqQkvRope), _vp]),
+    "cc_seq_turn_heads_gate": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _f32, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "cc_seq_softcap": (C.c_int, [_vp, _i64, _f32, _vp]),
 })
 
 _seq_lib = None

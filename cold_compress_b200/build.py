@@ -41,26 +41,40 @@ def seq_needs_build() -> bool:
 
 
 def build_seq_extension(force: bool = False, verbose: bool = False) -> Path:
-    """csrc/seq/*.cu -> libcc_b200_seq.so.  Safe when several processes start at once: the library is linked under a
-    temporary name and renamed into place."""
+    """csrc/seq/*.cu -> libcc_b200_seq.so: every file is compiled to its own object (in parallel), then linked.  Safe
+    when several processes start at once: objects and the library are written under temporary names (in a scratch
+    folder of their own) and the library is renamed into place."""
     if not force and not seq_needs_build():
         return SEQ_SO
     import os
+    import shutil
     import tempfile
-    flags = [f for f in NVCC_FLAGS if f != "-Xptxas" and f != "-v"]
-    fd, tmp = tempfile.mkstemp(dir=str(PKG), prefix=".libcc_b200_seq.", suffix=".so")
-    os.close(fd)
+    from concurrent.futures import ThreadPoolExecutor
+    flags = [f for f in NVCC_FLAGS if f not in ("-Xptxas", "-v", "--shared")]
+    work = Path(tempfile.mkdtemp(dir=str(PKG), prefix=".seq_build."))
     try:
-        res = subprocess.run(["nvcc", *flags, "-o", tmp, *[str(s) for s in seq_sources()]], capture_output=True, text=True)
-        if verbose or res.returncode:
-            sys.stderr.write(res.stdout + res.stderr)
-        if res.returncode:
+        def compile_one(src: Path):
+            obj = work / (src.stem + ".o")
+            res = subprocess.run(["nvcc", *flags, "-c", "-o", str(obj), str(src)], capture_output=True, text=True)
+            return res.returncode, res.stdout + res.stderr, obj
+
+        with ThreadPoolExecutor(max_workers=8) as ex:
+            results = list(ex.map(compile_one, seq_sources()))
+        logs = "".join(t for _, t, _ in results)
+        if verbose or any(rc for rc, _, _ in results):
+            sys.stderr.write(logs)
+        if any(rc for rc, _, _ in results):
             raise RuntimeError("nvcc failed building libcc_b200_seq.so")
+        tmp = work / "libcc_b200_seq.so"
+        res = subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "--shared", "-Xcompiler", "-fPIC", "-o", str(tmp),
+                              *[str(o) for _, _, o in results]], capture_output=True, text=True)
+        if res.returncode:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError("nvcc failed linking libcc_b200_seq.so")
         os.chmod(tmp, 0o755)
         os.replace(tmp, SEQ_SO)
     finally:
-        if os.path.exists(tmp):
-            os.unlink(tmp)
+        shutil.rmtree(work, ignore_errors=True)
     return SEQ_SO
 
 

@@ -230,23 +230,26 @@ class KVCache(nn.Module):
         None when this cache's policy does not keep a contiguous run of positions."""
         return None
 
-    def sequence_step(self, q, k_new, v_new, input_pos, y, window=0, sink=None, sink_mode=0, scale=1.0):
+    def sequence_step(self, q, k_new, v_new, input_pos, y, window=0, sink=None, sink_mode=0, scale=1.0, block=0):
         """Attention of T consecutive new tokens over the cache and themselves, then their append, with every key
         addressed by position: q [T, Hq, Dk] fp32 (normalised), k_new [T, H, Dk] / v_new [T, H, Dv] in the cache's
         dtype, input_pos int32 [1] = position of the first token (device), y [T, Hq, Dv] out.  Query p sees key j
-        when j <= p and (window == 0 or p - j < window).  T == 1 is one launch (keys split over CTAs, append fused);
+        when j <= p and (window == 0 or p - j < window) and (block == 0 or p // block == j // block).  T == 1 is one launch (keys split over CTAs, append fused);
         T > 1 (and groups of more than 16 query heads) is the tiled chunk kernel followed by the append kernel.  Nothing here synchronises with the host."""
         from . import seq_ops
         keep = self.sequence_window()
         if keep is None or self.quantize:
             raise _lib.CcError(f"{type(self).__name__} cannot serve position-addressed steps")
-        if (window == 0 and keep != 0) or (window > 0 and keep != 0 and keep < window):
-            raise _lib.CcError(f"cache keeps {keep} positions but the layer looks back {window or 'without limit'}")
+        reach = int(block) if block else int(window)      # the most positions a query looks back, 0 = without limit
+        if block and window:
+            raise _lib.CcError("a layer has a window or a block mask, not both")
+        if (reach == 0 and keep != 0) or (reach > 0 and keep != 0 and keep < reach):
+            raise _lib.CcError(f"cache keeps {keep} positions but the layer looks back {reach or 'without limit'}")
         T = q.shape[0]
         args = (q, k_new, v_new, self.k_cache, self.v_cache, self.pos, self.mask, self.cache_cts, input_pos, y, sink,
                 int(window), int(sink_mode), float(scale))
         if T == 1 and q.shape[1] <= 16 * self.n_heads:   # the one-token kernel holds up to 16 query heads per KV head
-            seq_ops.seq_attention(*args, seq_ops.ATTN_DECODE_APPEND, self._sequence_workspace(q.shape[1], window))
+            seq_ops.seq_attention(*args, seq_ops.ATTN_DECODE_APPEND, self._sequence_workspace(q.shape[1], reach), int(block))
         elif T == 1 and self.n_heads == 1:
             # many query heads over one shared row per position (latent rows): 16 heads per launch; every launch takes
             # the new key from k_new, the last one also appends it
@@ -256,10 +259,10 @@ class KVCache(nn.Module):
                 part = (q[:, h0:h1], k_new, v_new, self.k_cache, self.v_cache, self.pos, self.mask, self.cache_cts, input_pos,
                         y[:, h0:h1], None if sink is None else sink[h0:h1], int(window), int(sink_mode), float(scale))
                 seq_ops.seq_attention(*part, seq_ops.ATTN_DECODE_APPEND if h1 == H else seq_ops.ATTN_DECODE,
-                                      self._sequence_workspace(16, window))
+                                      self._sequence_workspace(16, reach), int(block))
         else:
-            seq_ops.seq_attention(*args, seq_ops.ATTN_CHUNK, None)
-            seq_ops.seq_attention(*args, seq_ops.ATTN_APPEND_ONLY, None)
+            seq_ops.seq_attention(*args, seq_ops.ATTN_CHUNK, None, int(block))
+            seq_ops.seq_attention(*args, seq_ops.ATTN_APPEND_ONLY, None, int(block))
         return y
 
     def _sequence_workspace(self, n_q_heads, window):
@@ -822,19 +825,22 @@ class KVCacheLatent(KVCacheFull):
 
 class RecurrentState(nn.Module):
     """What a sequence carries from token to token besides key/value rows: `vectors` fp32 [n_vectors, width]
-    (previous-token activations for token shift) and, for a layer with a matrix-state recurrence, `matrix` fp32
-    [n_heads, head_dim, head_dim].  Fixed size whatever the sequence length; `reset` gives it back (all zero = the
-    state before the first token).  Built through `get_cache_constructor("state")` like the caches."""
-    relevant_kwargs = ["state_vectors", "state_width", "max_seq_length"]
+    (previous-token activations for a token shift, or the last inputs of a short convolution) and, for a layer with a
+    matrix-state recurrence, `matrix` fp32 [n_heads, head_dim, state_cols] (state_cols defaults to head_dim).  Fixed
+    size whatever the sequence length; `reset` gives it back (all zero = the state before the first token).  Built
+    through `get_cache_constructor("state")` like the caches."""
+    relevant_kwargs = ["state_vectors", "state_width", "state_cols", "max_seq_length"]
 
-    def __init__(self, max_batch_size, n_heads, head_dim, dtype=torch.float32, state_vectors=1, state_width=0, **kwargs):
+    def __init__(self, max_batch_size, n_heads, head_dim, dtype=torch.float32, state_vectors=1, state_width=0, state_cols=None,
+                 **kwargs):
         super().__init__()
         if max_batch_size != 1:
             raise NotImplementedError("batch size is fixed to 1 (reference model.py:188-189)")
         self.n_heads, self.head_dim = int(n_heads), int(head_dim)
+        self.state_cols = int(state_cols) if state_cols else self.head_dim
         self.max_cache_length = 0   # holds no positions
         self.register_buffer("vectors", torch.zeros(int(state_vectors), int(state_width), dtype=torch.float32))
-        self.register_buffer("matrix", torch.zeros(self.n_heads, self.head_dim, self.head_dim, dtype=torch.float32)
+        self.register_buffer("matrix", torch.zeros(self.n_heads, self.head_dim, self.state_cols, dtype=torch.float32)
                              if n_heads else torch.zeros(0, dtype=torch.float32))
 
     def reset(self):

@@ -62,6 +62,9 @@ def _builtin():
     if "Detatar" not in MODEL_REGISTRY:
         from .detatar import DetatarTransformer
         register_model("Detatar", DetatarTransformer.from_config)
+    if "Tefovik" not in MODEL_REGISTRY:
+        from .tefovik import TefovikTransformer
+        register_model("Tefovik", TefovikTransformer.from_config)
 
 
 def is_checkpoint_folder(path) -> bool:

@@ -83,6 +83,7 @@ __device__ __forceinline__ float unit_act(float z, int kind) {
         case CC_ACT_SILU: return z * sigmoidf_(z);
         case CC_ACT_TANH: return tanhf(z);
         case CC_ACT_SIGMOID: return sigmoidf_(z);
+        case CC_ACT_RELU_SQ: { const float r = fmaxf(z, 0.f); return r * r; }
         default: return z;
     }
 }
@@ -946,7 +947,7 @@ int cc_seq_token_shift(const float* h, float* state, const float* mu, void* out,
 
 int cc_seq_gated_unit(const float* in, int64_t ld, int32_t off_gate, int32_t off_up, void* out, int32_t out_dtype,
                       int32_t T, int32_t F, int32_t kind, void* stream) {
-    if (!in || !out || T < 1 || F < 1 || kind < CC_ACT_NONE || kind > CC_ACT_SIGMOID)
+    if (!in || !out || T < 1 || F < 1 || kind < CC_ACT_NONE || kind > CC_ACT_LAST)
         return fail(CC_SEQ_ERR_INVALID_ARG, "gated_unit: bad argument");
     cudaStream_t st = (cudaStream_t)stream;
     const dim3 nb((F + 255) / 256, T < 4096 ? T : 4096);
@@ -1109,7 +1110,7 @@ int cc_seq_gemv_multi(const CcSeqGemvMulti* g, void* stream) {
     int blocks = 0, kmax = 0;
     for (int j = 0; j < g->n_jobs; ++j) {
         const CcSeqGemvJob& b = g->job[j];
-        if (!b.x || !b.W || !b.out || b.N < 1 || b.K < 1 || b.kind < CC_ACT_NONE || b.kind > CC_ACT_SIGMOID ||
+        if (!b.x || !b.W || !b.out || b.N < 1 || b.K < 1 || b.kind < CC_ACT_NONE || b.kind > CC_ACT_LAST ||
             ((b.kind != CC_ACT_NONE || b.off_up >= 0) && b.x_dtype != CC_DT_F32))
             return fail(CC_SEQ_ERR_INVALID_ARG, "gemv_multi: bad job");
         blocks += (b.N + 7) / 8;

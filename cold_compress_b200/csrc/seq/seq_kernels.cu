@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn
         return r < nq ? a.q + ((size_t)(i0 + r) * a.H + h) * Dk : nullptr;
     }, tid, ATT_THREADS);
     const int j_hi = p0 + i0 + nq - 1;
-    const int j_lo = a.window > 0 ? max(0, p0 + i0 - a.window + 1) : 0;
+    const int j_lo = a.block > 0 ? ((p0 + i0) / a.block) * a.block : (a.window > 0 ? max(0, p0 + i0 - a.window + 1) : 0);
 
     float m[4], l[4], O[4][4 * DV4];
 #pragma unroll
@@ -279,7 +279,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn
             for (int c = 0; c < 2; ++c) {
                 const int col = tx + 16 * c;
                 const int j = jt + col;
-                const bool ok = qi < nq && col < nk && ksrc[col] != -1 && j <= i && (a.window == 0 || i - j < a.window);
+                const bool ok = qi < nq && col < nk && ksrc[col] != -1 && j <= i && (a.window == 0 || i - j < a.window) &&
+                                (a.block == 0 || j >= (i / a.block) * a.block);
                 s[r][c] = ok ? s[r][c] * a.scale : -INFINITY;
                 mx = fmaxf(mx, s[r][c]);
             }
@@ -359,6 +360,9 @@ __host__ __device__ inline int decode_max_splits(int L, int window) {
     return (int)(tiles < DEC_MAX_SPLITS ? tiles : DEC_MAX_SPLITS);
 }
 
+// the most keys a query can see besides the limit of the cache: its window, or its block
+__host__ __device__ inline int attn_reach(const CcSeqAttn& a) { return a.block > 0 ? a.block : a.window; }
+
 template <typename CT>
 __device__ __forceinline__ void append_row(const CcSeqAttn& a, int g, int t, int p, int tid, int nthreads) {
     const int slot = p % a.L;
@@ -400,13 +404,13 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_decode_kernel(const CcSeqAtt
 
     const int sp = blockIdx.x, g = blockIdx.y, tid = threadIdx.x;
     const int p = a.input_pos[0];
-    const int j_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    const int j_lo = a.block > 0 ? (p / a.block) * a.block : (a.window > 0 ? max(0, p - a.window + 1) : 0);
     const int n = p - j_lo + 1;
     const int n_tiles = (n + KS - 1) / KS;
     const int tiles_per = (n_tiles + DEC_MAX_SPLITS - 1) / DEC_MAX_SPLITS;
     const int nsplit = (n_tiles + tiles_per - 1) / tiles_per;
     if (sp >= nsplit) return;
-    const int NS = decode_max_splits(a.L, a.window);
+    const int NS = decode_max_splits(a.L, attn_reach(a));
     int* counters = (int*)a.workspace;
     float* part_m = (float*)(counters + ((a.G + 3) & ~3));
     float* part_l = part_m + (size_t)a.G * NS * R;
@@ -846,6 +850,8 @@ static int check_attn(const CcSeqAttn* a) {
     if (a->Dk > 256 || a->Dv > 256) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "attention: head sizes above 256");
     if (a->window > 0 && a->L < a->window)
         return fail(CC_SEQ_ERR_INVALID_ARG, "attention: cache capacity below the window");
+    if (a->block < 0 || (a->block > 0 && (a->window > 0 || a->L < a->block)))
+        return fail(CC_SEQ_ERR_INVALID_ARG, "attention: a block mask needs a cache of at least one block and no window");
     if (a->sink_mode == CC_SINK_LEARNED && !a->sink) return fail(CC_SEQ_ERR_INVALID_ARG, "attention: sink missing");
     return CC_SEQ_OK;
 }
@@ -888,7 +894,7 @@ static int launch_decode_r(const CcSeqAttn* a, cudaStream_t st) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail(CC_SEQ_ERR_CUDA, cudaGetErrorString(e));
     }
-    dim3 grid(decode_max_splits(a->L, a->window), a->G);
+    dim3 grid(decode_max_splits(a->L, attn_reach(*a)), a->G);
     kern<<<grid, DEC_THREADS, smem, st>>>(*a);
     return cuda_check("attn_decode_kernel");
 }
@@ -971,7 +977,7 @@ int cc_seq_attention_decode(const CcSeqAttn* a, void* stream) {
     int rc = check_attn(a);
     if (rc) return rc;
     if (a->T != 1) return fail(CC_SEQ_ERR_INVALID_ARG, "attention_decode: one token per call");
-    if (!a->workspace || a->workspace_bytes < cc_seq_decode_workspace(a->H, a->G, a->Dv, a->L, a->window))
+    if (!a->workspace || a->workspace_bytes < cc_seq_decode_workspace(a->H, a->G, a->Dv, a->L, attn_reach(*a)))
         return fail(CC_SEQ_ERR_INVALID_ARG, "attention_decode: workspace missing or too small");
     cudaStream_t st = (cudaStream_t)stream;
 #define CALL(CT, YT) launch_decode<CT, YT>(a, st)

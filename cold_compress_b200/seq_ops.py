@@ -24,7 +24,7 @@ _library.define("seq_qkv_prepare(Tensor qkv, Tensor? bias, Tensor input_pos, Ten
                 "float gain_coef, int gain_every) -> ()")
 _library.define("seq_attention(Tensor q, Tensor k_new, Tensor v_new, Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor(c!) pos, "
                 "Tensor(d!) mask, Tensor(e!) cache_cts, Tensor input_pos, Tensor(f!) y, Tensor? sink, int window, "
-                "int sink_mode, float scale, int mode, Tensor(g!)? workspace) -> ()")
+                "int sink_mode, float scale, int mode, Tensor(g!)? workspace, int block=0) -> ()")
 _library.define("seq_residual_norm(Tensor(a!) x, Tensor? y, Tensor w, float alpha, float eps, Tensor(b!)? x_act) -> ()")
 _library.define("seq_clamped_glu(Tensor gu, Tensor(a!) out, float limit, float slope) -> ()")
 _library.define("seq_gemv(Tensor x, Tensor? in_norm_w, Tensor w, Tensor? bias, Tensor? res, Tensor? res_norm_w, Tensor(a!) out, "
@@ -83,7 +83,7 @@ def _seq_qkv_prepare(qkv, bias, input_pos, mix_lambda, v_first, q, k, v, H, G, D
 
 
 def _seq_attention(q, k_new, v_new, k_cache, v_cache, pos, mask, cache_cts, input_pos, y, sink, window, sink_mode, scale,
-                   mode, workspace):
+                   mode, workspace, block=0):
     _need(("q", q, torch.float32), ("k_new", k_new, k_cache.dtype), ("v_new", v_new, k_cache.dtype), ("k_cache", k_cache, None),
           ("v_cache", v_cache, k_cache.dtype), ("pos", pos, torch.int32), ("mask", mask, torch.bool),
           ("cache_cts", cache_cts, torch.int32), ("input_pos", input_pos, torch.int32), ("y", y, None),
@@ -99,6 +99,7 @@ def _seq_attention(q, k_new, v_new, k_cache, v_cache, pos, mask, cache_cts, inpu
     a.T, a.H, a.G, a.Dk, a.Dv, a.L = T, H, G, Dk, Dv, L
     a.window, a.sink_mode, a.cache_dtype, a.y_dtype, a.scale = int(window), int(sink_mode), _dt(k_cache), _dt(y), float(scale)
     a.append = int(mode == ATTN_DECODE_APPEND)
+    a.block = int(block)
     if workspace is not None:
         a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
     lib = _lib.load_seq()
@@ -444,3 +445,118 @@ def gemv_multi(jobs):
         b.x, b.W, b.out = _p(x), _p(w), _p(out)
         b.x_dtype, b.kind, b.off_gate, b.off_up, b.N, b.K = _dt(x), int(kind), int(off_gate), int(off_up), N, K
     _lib.check_seq(_lib.load_seq().cc_seq_gemv_multi(C.byref(g), _stream()), "cc_seq_gemv_multi")
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Third part of the C ABI (csrc/seq/scan_kernels.cu): norms after the sum, short convolutions with a carried tail,
+# matrix-state scans, gated group norms, rotations of heads, the logit soft cap.
+
+def sum_norm(w, eps, x=None, y=None, y_norm_w=None, y2=None, y2_norm_w=None, y_coef=1.0, y_scale=None, alpha=1.0,
+             center=True, gain_offset=0.0, out=None, out_act=None, stack=None, n_prev=0, coef=None, mix=None, rows=None):
+    """n = norm(alpha * x + y_scale * y_coef * (y' + y2')) * (w + gain_offset), y' = y or its RMS norm times y_norm_w;
+    out <- n; with coef: mix <- sum_j<n_prev coef[j] * stack[j] + coef[n_prev] * n; out_act <- mix (or n) in its dtype.
+    `rows` (int64) selects input rows; outputs are compact."""
+    _need(("w", w, torch.float32), ("x", x, torch.float32), ("y_norm_w", y_norm_w, torch.float32), ("y2_norm_w", y2_norm_w, torch.float32),
+          ("y_scale", y_scale, torch.float32), ("out", out, torch.float32), ("out_act", out_act, None), ("stack", stack, torch.float32),
+          ("coef", coef, torch.float32), ("mix", mix, torch.float32), ("rows", rows, torch.int64))
+    a = _lib.CcSeqSumNorm()
+    E = w.numel()
+    ref = x if x is not None else y
+    a.T = rows.numel() if rows is not None else ref.shape[0]
+    a.E = E
+    a.x, a.w, a.y_norm_w, a.y2_norm_w, a.y_scale = _p(x), _p(w), _p(y_norm_w), _p(y2_norm_w), _p(y_scale)
+    a.y, a.ldy = _cols(_f32("y", y))
+    a.y2, a.ldy2 = _cols(_f32("y2", y2))
+    a.y_coef, a.alpha, a.eps, a.gain_offset, a.center = float(y_coef), float(alpha), float(eps), float(gain_offset), int(bool(center))
+    a.out, a.out_act, a.rows = _p(out), _p(out_act), _p(rows)
+    a.act_dtype = _dt(out_act) if out_act is not None else _lib.DT_F32
+    if coef is not None:
+        assert mix is not None and coef.numel() >= n_prev + 1 and (n_prev == 0 or stack is not None)
+        a.stack, a.stack_stride, a.n_prev, a.coef, a.mix = _p(stack), (stack.stride(0) if stack is not None else 0), int(n_prev), _p(coef), _p(mix)
+    _lib.check_seq(_lib.load_seq().cc_seq_sum_norm(C.byref(a), _stream()), "cc_seq_sum_norm")
+
+
+def short_conv(u, w, bias, tail, out, act=_lib.ACT_NONE):
+    """out[t, c] = act(bias[c] + sum_j w[c, j] * u[t - taps + 1 + j, c]) with the inputs before this call in `tail`
+    [taps - 1, C], which is then moved on.  u / out: fp32 column ranges [T, C]."""
+    _need(("w", w, torch.float32), ("bias", bias, torch.float32), ("tail", tail, torch.float32))
+    up, ldu = _cols(_f32("u", u))
+    op, ldo = _cols(_f32("out", out))
+    T, Cn = u.shape
+    taps = w.shape[1]
+    assert w.shape[0] == Cn and out.shape == u.shape and (taps == 1 or tail.shape == (taps - 1, Cn))
+    _lib.check_seq(_lib.load_seq().cc_seq_short_conv(up, ldu, _p(w), _p(bias), _p(tail), op, ldo, T, Cn, taps, int(act), _stream()),
+                   "cc_seq_short_conv")
+
+
+def ssd_scan(x, B, Cm, dt_raw, dt_bias, A_log, D, state, y, H, G, N, V):
+    """State-space scan over T tokens: x [T, H*V], B / Cm [T, G*N], dt_raw [T, H] (fp32 column ranges), state fp32
+    [H, N, V] carried, y fp32 [T, H*V]."""
+    _need(("dt_bias", dt_bias, torch.float32), ("A_log", A_log, torch.float32), ("D", D, torch.float32), ("state", state, torch.float32),
+          ("y", y, torch.float32))
+    a = _lib.CcSeqSsdScan()
+    a.x, a.ldx = _cols(_f32("x", x))
+    a.B, a.ldbc = _cols(_f32("B", B))
+    a.C, ldc = _cols(_f32("C", Cm))
+    a.dt_raw, a.lddt = _cols(_f32("dt_raw", dt_raw))
+    assert ldc == a.ldbc and state.numel() == H * N * V and y.shape == (x.shape[0], H * V)
+    a.dt_bias, a.A_log, a.D, a.state, a.y = _p(dt_bias), _p(A_log), _p(D), _p(state), _p(y)
+    a.T, a.H, a.G, a.N, a.V = x.shape[0], int(H), int(G), int(N), int(V)
+    _lib.check_seq(_lib.load_seq().cc_seq_ssd_scan(C.byref(a), _stream()), "cc_seq_ssd_scan")
+
+
+def delta_scan(q, k, v, beta_raw, a_raw, dt_bias, A_log, state, o, H, G, D, V, q_scale, unit_eps=1e-6):
+    """Delta rule with a decay per key channel over T tokens: q / k [T, G*D], v [T, H*V], beta_raw [T, H], a_raw
+    [T, H*D] (fp32 column ranges), state fp32 [H, D, V] carried, o fp32 [T, H*V]."""
+    _need(("dt_bias", dt_bias, torch.float32), ("A_log", A_log, torch.float32), ("state", state, torch.float32), ("o", o, torch.float32))
+    a = _lib.CcSeqDeltaScan()
+    a.q, a.ldqk = _cols(_f32("q", q))
+    a.k, ldk = _cols(_f32("k", k))
+    a.v, a.ldv = _cols(_f32("v", v))
+    a.beta_raw, a.ldb = _cols(_f32("beta_raw", beta_raw))
+    a.a_raw, a.lda = _cols(_f32("a_raw", a_raw))
+    assert ldk == a.ldqk and state.numel() == H * D * V and o.shape == (q.shape[0], H * V) and dt_bias.numel() == H * D
+    a.dt_bias, a.A_log, a.state, a.o = _p(dt_bias), _p(A_log), _p(state), _p(o)
+    a.T, a.H, a.G, a.D, a.V = q.shape[0], int(H), int(G), int(D), int(V)
+    a.q_scale, a.unit_eps = float(q_scale), float(unit_eps)
+    _lib.check_seq(_lib.load_seq().cc_seq_delta_scan(C.byref(a), _stream()), "cc_seq_delta_scan")
+
+
+def gated_rms_groups(y, gate, gate_act, gate_first, w, out, groups, eps):
+    """out = group-wise RMS norm of y [T, W] times w[col mod len(w)], gated by act(gate) before or after the norm."""
+    _need(("y", y, torch.float32), ("w", w, torch.float32), ("out", out, None))
+    gp, ldg = _cols(_f32("gate", gate))
+    T, W = y.shape
+    _lib.check_seq(_lib.load_seq().cc_seq_gated_rms_groups(_p(y), gp, ldg, int(gate_act), int(bool(gate_first)), _p(w), w.numel(),
+                                                           _p(out), _dt(out), T, W, int(groups), float(eps), _stream()),
+                   "cc_seq_gated_rms_groups")
+
+
+def qkv_rope(src, off_q, off_k, off_v, H, G, Dk, Dv, q_norm_w, k_norm_w, eps, rot_dims, interleaved, inv_freq, v_inv_freq,
+             input_pos, q_out, k_out, v_out):
+    _need(("q_norm_w", q_norm_w, torch.float32), ("k_norm_w", k_norm_w, torch.float32), ("inv_freq", inv_freq, torch.float32),
+          ("v_inv_freq", v_inv_freq, torch.float32), ("input_pos", input_pos, torch.int32), ("q_out", q_out, torch.float32),
+          ("k_out", k_out, None), ("v_out", v_out, k_out.dtype))
+    a = _lib.CcSeqQkvRope()
+    a.inp, a.ld = _cols(_f32("src", src))
+    a.off_q, a.off_k, a.off_v, a.H, a.G, a.Dk, a.Dv = int(off_q), int(off_k), int(off_v), int(H), int(G), int(Dk), int(Dv)
+    a.q_norm_w, a.k_norm_w, a.eps, a.rot_dims, a.interleaved = _p(q_norm_w), _p(k_norm_w), float(eps), int(rot_dims), int(bool(interleaved))
+    assert (rot_dims == 0 or inv_freq.numel() >= rot_dims // 2) and (v_inv_freq is None or (Dv % 2 == 0 and v_inv_freq.numel() >= Dv // 2))
+    a.inv_freq, a.v_inv_freq, a.input_pos = _p(inv_freq), _p(v_inv_freq), _p(input_pos)
+    a.q_out, a.k_out, a.v_out, a.out_dtype, a.T = _p(q_out), _p(k_out), _p(v_out), _dt(k_out), src.shape[0]
+    _lib.check_seq(_lib.load_seq().cc_seq_qkv_rope(C.byref(a), _stream()), "cc_seq_qkv_rope")
+
+
+def turn_heads_gate(y, input_pos, inv_freq, dims, interleaved, sign, gate, out):
+    """out[t, h] = turn(y[t, h], sign * position) * sigmoid(gate[t, h]); y fp32 [T, H, Dv]."""
+    _need(("y", y, torch.float32), ("input_pos", input_pos, torch.int32), ("inv_freq", inv_freq, torch.float32), ("out", out, None))
+    gp, ldg = _cols(_f32("gate", gate))
+    T, H, Dv = y.shape
+    _lib.check_seq(_lib.load_seq().cc_seq_turn_heads_gate(_p(y), _p(input_pos), _p(inv_freq), int(dims), int(bool(interleaved)),
+                                                          float(sign), gp, ldg, _p(out), _dt(out), T, H, Dv, _stream()),
+                   "cc_seq_turn_heads_gate")
+
+
+def softcap(x, cap):
+    _need(("x", x, torch.float32))
+    _lib.check_seq(_lib.load_seq().cc_seq_softcap(_p(x), x.numel(), float(cap), _stream()), "cc_seq_softcap")

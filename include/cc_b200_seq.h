@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define CC_SEQ_ABI_VERSION 2
+#define CC_SEQ_ABI_VERSION 3
 
 #define CC_SEQ_OK                     0
 #define CC_SEQ_ERR_INVALID_ARG       -1
@@ -39,7 +39,8 @@ extern "C" {
 
 /*
  * One attention layer's step over a chunk of T consecutive tokens whose first position is *input_pos.
- * Query i (position p = *input_pos + i) sees key position j when j <= p and (window == 0 or p - j < window).
+ * Query i (position p = *input_pos + i) sees key position j when j <= p and (window == 0 or p - j < window) and
+ * (block == 0 or floor(p / block) == floor(j / block)): blocks are counted from position 0 of the sequence.
  * Keys j >= *input_pos are rows of k_new / v_new; older keys are read from cache slot j mod L and count only if
  * pos[slot] == j (an empty, stale or overwritten slot is not a key).
  */
@@ -63,6 +64,7 @@ typedef struct CcSeqAttn {
     int32_t append;            /* decode only (T == 1): also write the new row into its slot */
     void* workspace;           /* decode only: cc_seq_decode_workspace() bytes, zeroed once by the caller */
     uint64_t workspace_bytes;
+    int32_t block;             /* 0 = none; else keys of the query's own block of `block` positions only (L >= block) */
 } CcSeqAttn;
 
 int cc_seq_abi_version(void);
@@ -89,6 +91,7 @@ int cc_seq_attention(const CcSeqAttn* a, void* stream);
 /* T == 1: keys split over CTAs, partial results combined in split order by the last CTA of a head; with
  * a->append the new row is written to slot p mod L (k, v, pos, mask, cache_cts) by the same launch. */
 int cc_seq_attention_decode(const CcSeqAttn* a, void* stream);
+/* `window`: the layer's window, or its block size when it has one (the most keys a token can see; 0 = all) */
 uint64_t cc_seq_decode_workspace(int32_t H, int32_t G, int32_t Dv, int32_t L, int32_t window);
 /* Writes rows of k_new / v_new into slots (p mod L); of a chunk longer than L only the last L rows. */
 int cc_seq_cache_append(const CcSeqAttn* a, void* stream);
@@ -146,6 +149,8 @@ int cc_seq_gemv(const CcSeqGemv* g, void* stream);
 #define CC_ACT_SILU       2  /* z sigmoid(z) */
 #define CC_ACT_TANH       3
 #define CC_ACT_SIGMOID    4
+#define CC_ACT_RELU_SQ    5  /* max(z, 0)^2 */
+#define CC_ACT_LAST       5
 
 /* x[t] = embed[tok[t]] * scale, fp32 [T, E] */
 int cc_seq_embed_rows(const int32_t* tokens, const void* embed, int32_t table_dtype, float* x, int32_t T, int32_t E,
@@ -312,6 +317,123 @@ typedef struct CcSeqMoeCombine {
     int32_t T, E, top, n_real;
 } CcSeqMoeCombine;
 int cc_seq_moe_combine(const CcSeqMoeCombine* a, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Third part (csrc/seq/scan_kernels.cu): post-sum norms with layer scale and a weighted average over the depth,
+ * short causal convolutions with a carried tail, two matrix-state recurrences (a state-space scan with a scalar decay
+ * per head, and a delta rule with a decay per key channel), gated group norms, and rotations of query, key and value
+ * heads.  fp32 arithmetic throughout; inputs named "fp32 [T, ld]" are column ranges of wider rows.
+ * ------------------------------------------------------------------------------------------------------------------ */
+
+/*
+ * Norm after the sum.  Per row t (row rows[t] of x / y / y2 when `rows` is given; outputs are compact in t):
+ *   r = y                                   (plain)     or  y / sqrt(mean(y^2) + eps) * y_norm_w   (y_norm_w set)
+ *   r = y_coef * (r + the same of y2)        (y2 set; y_coef multiplies also without y2)
+ *   s = alpha * x + y_scale * r              (x, y, y_scale each optional)
+ *   n = (s - mean(s)) / sqrt(mean((s - mean(s))^2) + eps) * (w + gain_offset)     (center != 0)
+ *     =  s / sqrt(mean(s^2) + eps) * (w + gain_offset)                             (center == 0)
+ *   out[t] = n;  with coef:  mix[t] = sum_{j < n_prev} coef[j] * stack[j * stack_stride + t * E ...] + coef[n_prev] * n
+ *   out_act[t] = mix[t] if coef else n, in act_dtype.
+ */
+typedef struct CcSeqSumNorm {
+    const float* x;
+    const float* y;   int64_t ldy;   const float* y_norm_w;
+    const float* y2;  int64_t ldy2;  const float* y2_norm_w;
+    float y_coef;
+    const float* y_scale;
+    const float* w;
+    float alpha, eps, gain_offset;
+    int32_t center;
+    float* out;
+    const float* stack;  int64_t stack_stride;  int32_t n_prev;  const float* coef;  float* mix;
+    void* out_act;  int32_t act_dtype;
+    const int64_t* rows;
+    int32_t T, E;
+} CcSeqSumNorm;
+int cc_seq_sum_norm(const CcSeqSumNorm* a, void* stream);
+
+/*
+ * Causal convolution over time on each of C channels: out[t, c] = act(bias[c] + sum_j w[c, j] * u[t - taps + 1 + j, c]),
+ * where u[-k] for k = 1 .. taps-1 is tail[taps - 1 - k, c] (the inputs that came before this call; zeros at a
+ * sequence's start).  Afterwards tail holds the last taps - 1 inputs.  u fp32 [T, ldu], w fp32 [C, taps], out fp32
+ * [T, ldo], tail fp32 [taps - 1, C]; bias may be NULL; act is a CC_ACT_* kind.  taps >= 1.
+ */
+int cc_seq_short_conv(const float* u, int64_t ldu, const float* w, const float* bias, float* tail, float* out,
+                      int64_t ldo, int32_t T, int32_t C, int32_t taps, int32_t act, void* stream);
+
+/*
+ * State-space scan, one state S [N, V] per head (head h reads group h / (H / G) of B and C):
+ *   dt = softplus(dt_raw + dt_bias[h]);  a = exp(-exp(A_log[h]) * dt)
+ *   S <- a * S + dt * B_t x_t^T;   y_t = S^T C_t + D[h] * x_t
+ * x fp32 [T, ldx] (H * V columns), B, C fp32 [T, ldbc] (G * N columns each), dt_raw fp32 [T, lddt] (H columns),
+ * y fp32 [T, H * V] contiguous, state fp32 [H, N, V] read and written.  Exactly sequential in t.
+ */
+typedef struct CcSeqSsdScan {
+    const float* x;  int64_t ldx;
+    const float* B;  const float* C;  int64_t ldbc;
+    const float* dt_raw;  int64_t lddt;
+    const float* dt_bias;  const float* A_log;  const float* D;
+    float* state;  float* y;
+    int32_t T, H, G, N, V;
+} CcSeqSsdScan;
+int cc_seq_ssd_scan(const CcSeqSsdScan* a, void* stream);
+
+/*
+ * Delta rule with a decay per key channel, one state S [D, V] per head (head h reads q / k head h / (H / G)):
+ *   qn = q / sqrt(sum(q^2) + unit_eps) * q_scale;  kn = k / sqrt(sum(k^2) + unit_eps);  beta = sigmoid(beta_raw)
+ *   g[i] = exp(-exp(A_log[h]) * softplus(a_raw[h * D + i] + dt_bias[h * D + i]))
+ *   S <- diag(g) S;  u = beta * (v - S^T kn);  S <- S + kn u^T;  o = S^T qn
+ * q, k fp32 [T, ldqk] (G * D columns), v fp32 [T, ldv] (H * V), beta_raw fp32 [T, ldb] (H), a_raw fp32 [T, lda]
+ * (H * D), o fp32 [T, H * V] contiguous, state fp32 [H, D, V] read and written.  Exactly sequential in t.
+ */
+typedef struct CcSeqDeltaScan {
+    const float* q;  const float* k;  int64_t ldqk;
+    const float* v;  int64_t ldv;
+    const float* beta_raw;  int64_t ldb;
+    const float* a_raw;  int64_t lda;
+    const float* dt_bias;  const float* A_log;
+    float* state;  float* o;
+    int32_t T, H, G, D, V;
+    float q_scale, unit_eps;
+} CcSeqDeltaScan;
+int cc_seq_delta_scan(const CcSeqDeltaScan* a, void* stream);
+
+/*
+ * Rows y fp32 [T, W] in `groups` equal consecutive parts, each divided by its root mean square, times w[col mod
+ * w_len], with a gate act(gate[t, col]) applied before the norm (gate_first != 0: the norm sees the gated values) or
+ * after it.  gate fp32 [T, ldg] or NULL; out [T, W] in out_dtype.
+ */
+int cc_seq_gated_rms_groups(const float* y, const float* gate, int64_t ldg, int32_t gate_act, int32_t gate_first,
+                            const float* w, int32_t w_len, void* out, int32_t out_dtype, int32_t T, int32_t W,
+                            int32_t groups, float eps, void* stream);
+
+/*
+ * Query, key and value heads of T tokens from fp32 rows `in` [T, ld] (q at off_q: H heads of Dk, k at off_k: G heads
+ * of Dk, v at off_v: G heads of Dv).  q and k heads: divided by their root mean square times q_norm_w / k_norm_w
+ * ([Dk], when set), then the first rot_dims entries turned by the angle p * inv_freq[i] for pair i, p = *input_pos + t;
+ * v heads: all Dv entries turned by p * v_inv_freq[m] (when set).  Pairs are (2i, 2i + 1) when interleaved, else
+ * (i, i + dims / 2).  A pair (a, b) becomes (a cos - b sin, b cos + a sin).  q_out fp32, k_out / v_out in out_dtype.
+ */
+typedef struct CcSeqQkvRope {
+    const float* in;  int64_t ld;
+    int32_t off_q, off_k, off_v, H, G, Dk, Dv;
+    const float* q_norm_w;  const float* k_norm_w;  float eps;
+    int32_t rot_dims, interleaved;
+    const float* inv_freq;  const float* v_inv_freq;
+    const int32_t* input_pos;
+    float* q_out;  void* k_out;  void* v_out;  int32_t out_dtype;
+    int32_t T;
+} CcSeqQkvRope;
+int cc_seq_qkv_rope(const CcSeqQkvRope* a, void* stream);
+
+/* out[t, h, :] = turn(y[t, h, :], sign * p * inv_freq) * sigmoid(gate[t * ldg + h]): the first `dims` entries of each
+ * head are turned (pairs as above), p = *input_pos + t; gate may be NULL.  y fp32 [T, H, Dv], out in out_dtype. */
+int cc_seq_turn_heads_gate(const float* y, const int32_t* input_pos, const float* inv_freq, int32_t dims,
+                           int32_t interleaved, float sign, const float* gate, int64_t ldg, void* out,
+                           int32_t out_dtype, int32_t T, int32_t H, int32_t Dv, void* stream);
+
+/* x <- cap * tanh(x / cap), fp32, n elements, in place */
+int cc_seq_softcap(float* x, int64_t n, float cap, void* stream);
 
 #ifdef __cplusplus
 }
