@@ -741,6 +741,41 @@ def _detatar_model(sz, extra, device, dtype):
     return model.eval()
 
 
+def _tefovik_config(sz):
+    """State-space layers (inner = 2 x width in heads of 64 value columns, 128 state rows, no feed-forward) alternate
+    with parallel layers: block-masked attention of the shape's heads (block = the shape's window, half of each head
+    rotated) beside a delta rule with half as many heads of 128 x 128, and the shape's dense feed-forward."""
+    E, D = sz["width"], sz["head"]
+    mamba = {"heads": 2 * E // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}
+    left = {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": D, "vdim": D, "conv": 4, "mask": {"size": sz["window"]},
+            "rot": {"base": 10000.0, "dims": D // 2}, "scale": D ** -0.5}
+    right = {"heads": sz["heads"] // 2, "kv_heads": sz["heads"] // 2, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}
+    layers = [{"type": "mamba2", "mixer": mamba, "mlp": None} if i % 2 == 0 else
+              {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": {"kind": "dense", "ff": sz["ff"]}} for i in range(sz["layers"])]
+    return {"architecture": "Tefovik", "vocab": sz["vocab"], "width": E, "norm": {"eps": 1e-5}, "postln_alpha": 2.0,
+            "logit_softcap": 30.0, "layers": layers}
+
+
+def _tefovik_model(sz, device, dtype):
+    from cold_compress_b200.tefovik import TefovikTransformer
+    with torch.device(device):
+        model = TefovikTransformer.from_config(_tefovik_config(sz), dtype)
+    gen = torch.Generator(device=device).manual_seed(0)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if name.endswith("conv.weight"):
+                p.fill_(1.0 / p.shape[1])
+            elif p.dim() >= 2:
+                p.copy_(torch.empty(p.shape, device=device).normal_(0.0, 0.02, generator=gen))
+            elif name.endswith("depth_coef"):
+                p.fill_(1.0 / p.numel())
+            elif name.endswith(("A_log", "dt_bias", "conv.bias")):
+                p.zero_()
+            else:
+                p.fill_(1.0)
+    return model.eval()
+
+
 def _llama_model(sz, device):
     from cold_compress_b200.model import ModelArgs, Transformer
     cfg = ModelArgs(block_size=sz["prompt"] + 1024, vocab_size=sz["vocab"], n_layer=sz["layers"], n_head=sz["heads"],
@@ -784,7 +819,7 @@ def run_design(args):
     names = [n for n in args.design.split(",") if n]
     flush = torch.zeros(64 << 20, dtype=torch.float32, device=device)
     rows = []
-    arms = ("detatar", "tidelorn") if args.design_model == "detatar" else ("tidelorn", "llama")
+    arms = {"detatar": ("detatar", "tidelorn"), "tefovik": ("tefovik", "detatar")}.get(args.design_model, ("tidelorn", "llama"))
     for name in names:
         sz = DESIGN_SIZES[name]
         P = sz["prompt"]
@@ -792,6 +827,7 @@ def run_design(args):
         row = {"size": name, **sz}
         for arm in arms:
             model = (_detatar_model(sz, DETATAR_SIZES[name], device, torch.bfloat16) if arm == "detatar" else
+                     _tefovik_model(sz, device, torch.bfloat16) if arm == "tefovik" else
                      _tidelorn_model(sz, device, torch.bfloat16) if arm == "tidelorn" else _llama_model(sz, device))
             ck = cache_kwargs(dict(slots=1.0, pattern="tile", strategy="full", compressor="recent_global"))
             ck["global_tokens"] = 0
@@ -839,10 +875,13 @@ def run_design(args):
             del model, decoder
             torch.cuda.empty_cache()
         row["kernels"] = _design_kernels(sz, device, hbm)
-        if args.design_model == "detatar":
+        if args.design_model in ("detatar", "tefovik"):
             row["detatar_kernels"] = _detatar_kernels(sz, DETATAR_SIZES[name], device, hbm)
+        if args.design_model == "tefovik":
+            row["tefovik_kernels"] = _tefovik_kernels(sz, device, hbm)
         rows.append(row)
     metric = ("prefill and decode tokens/s, Detatar beside Tidelorn at equal layer shape" if args.design_model == "detatar" else
+              "prefill and decode tokens/s, Tefovik beside Detatar at equal layer shape" if args.design_model == "tefovik" else
               "prefill and decode tokens/s, Tidelorn beside Llama (full cache) at equal layer shape")
     print(json.dumps({"metric": metric,
                       "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "steps": args.steps, "sizes": rows,
@@ -956,6 +995,76 @@ def _detatar_kernels(sz, extra, device, hbm):
     return out
 
 
+def _tefovik_kernels(sz, device, hbm):
+    """The Tefovik kernels alone at this shape: both matrix-state scans over a whole prompt and for one token, and the
+    block-masked attention over a prompt and for one token over its ring."""
+    from cold_compress_b200 import seq_ops
+    from cold_compress_b200.cache import get_cache_constructor
+    cfg = _tefovik_config(sz)
+    P = sz["prompt"]
+    gen = torch.Generator(device=device).manual_seed(4)
+    out = {}
+
+    def token_us(fn):
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(20):
+                fn()
+        return _time_events(graph.replay, 2, 5) * 1e3 / 20
+
+    m = cfg["layers"][0]["mixer"]
+    H, V, N = m["heads"], m["vdim"], m["state"]
+    x, B, C = (torch.randn(P, w, device=device, generator=gen) * 0.1 for w in (H * V, N, N))
+    dt_raw = torch.randn(P, H, device=device, generator=gen)
+    zeros, ones = torch.zeros(H, device=device), torch.ones(H, device=device)
+    state, y = torch.zeros(H, N, V, device=device), torch.empty(P, H * V, device=device)
+    ms = _time_events(lambda: seq_ops.ssd_scan(x, B, C, dt_raw, zeros, zeros, ones, state, y, H, 1, N, V), 2, 3)
+    out["state_space_scan_prompt"] = {"ms": round(ms, 3), "fp32_tflops": round(4.0 * P * H * N * V / ms / 1e9, 2),
+                                      "gb_per_s": round((2.0 * H * V + 2 * N + H) * P * 4 / ms / 1e6, 1)}
+    us = token_us(lambda: seq_ops.ssd_scan(x[:1], B[:1], C[:1], dt_raw[:1], zeros, zeros, ones, state, y[:1], H, 1, N, V))
+    nbytes = 2 * H * N * V * 4
+    out["state_space_scan_token"] = {"us": round(us, 2), "gb_per_s": round(nbytes / us / 1e3, 1), "frac_of_hbm": round(nbytes / us / 1e3 / hbm, 3)}
+    r = cfg["layers"][1]["mixer"]["right"]
+    H, D, V = r["heads"], r["dim"], r["vdim"]
+    q, k = (torch.randn(P, H * D, device=device, generator=gen) for _ in range(2))
+    v, a_raw = torch.randn(P, H * V, device=device, generator=gen) * 0.1, torch.randn(P, H * D, device=device, generator=gen)
+    beta = torch.randn(P, H, device=device, generator=gen)
+    dtb, alog = torch.zeros(H * D, device=device), torch.zeros(H, device=device)
+    state, o = torch.zeros(H, D, V, device=device), torch.empty(P, H * V, device=device)
+    ms = _time_events(lambda: seq_ops.delta_scan(q, k, v, beta, a_raw, dtb, alog, state, o, H, H, D, V, D ** -0.5), 2, 3)
+    out["delta_rule_scan_prompt"] = {"ms": round(ms, 3), "fp32_tflops": round(7.0 * P * H * D * V / ms / 1e9, 2),
+                                     "gb_per_s": round((3.0 * H * D + 2 * H * V + H) * P * 4 / ms / 1e6, 1)}
+    us = token_us(lambda: seq_ops.delta_scan(q[:1], k[:1], v[:1], beta[:1], a_raw[:1], dtb, alog, state, o[:1], H, H, D, V, D ** -0.5))
+    nbytes = 2 * H * D * V * 4
+    out["delta_rule_scan_token"] = {"us": round(us, 2), "gb_per_s": round(nbytes / us / 1e3, 1), "frac_of_hbm": round(nbytes / us / 1e3 / hbm, 3)}
+    l = cfg["layers"][1]["mixer"]["left"]
+    H, G, D, block = l["heads"], l["kv_heads"], l["dim"], l["mask"]["size"]
+    q = torch.randn(P, H, D, device=device, generator=gen)
+    k, v = (torch.randn(P, G, D, device=device, generator=gen).to(torch.bfloat16) for _ in range(2))
+    y = torch.empty(P, H, D, device=device)
+    ctor, _ = get_cache_constructor("recent_global")
+    with torch.device(device):
+        cache = ctor(1, G, D, torch.bfloat16, max_cache_length=block, global_tokens=0, max_seq_length=P + 8, cache_bits=None)
+    ip0 = torch.zeros(1, dtype=torch.int32, device=device)
+    args = (q, k, v, cache.k_cache, cache.v_cache, cache.pos, cache.mask, cache.cache_cts, ip0, y, None, 0, 0, D ** -0.5)
+    ms = _time_events(lambda: seq_ops.seq_attention(*args, seq_ops.ATTN_CHUNK, None, block), 2, 3)
+    pairs = sum((i % block) + 1 for i in range(P))
+    out["prefill_attention_block"] = {"ms": round(ms, 3), "fp32_tflops": round(4 * pairs * D * H / ms / 1e9, 2)}
+    seq_ops.seq_attention(*args, seq_ops.ATTN_APPEND_ONLY, None, block)
+    ipd = torch.tensor([P + block - 1], dtype=torch.int32, device=device)      # the last position of a block: a full ring of keys
+    seq_ops.seq_attention(q[:block - 1].contiguous(), k[:block - 1].contiguous(), v[:block - 1].contiguous(), cache.k_cache, cache.v_cache,
+                          cache.pos, cache.mask, cache.cache_cts, torch.tensor([P], dtype=torch.int32, device=device), y[:block - 1], None, 0, 0,
+                          D ** -0.5, seq_ops.ATTN_APPEND_ONLY, None, block)
+    ws = cache._sequence_workspace(H, block)
+    dargs = (q[:1], k[:1], v[:1], cache.k_cache, cache.v_cache, cache.pos, cache.mask, cache.cache_cts, ipd, y[:1], None, 0, 0, D ** -0.5)
+    us = token_us(lambda: seq_ops.seq_attention(*dargs, seq_ops.ATTN_DECODE, ws, block))
+    nbytes = 2 * G * block * D * 2
+    out["decode_attention_block"] = {"us": round(us, 2), "gb_per_s": round(nbytes / us / 1e3, 1), "frac_of_hbm": round(nbytes / us / 1e3 / hbm, 3)}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -968,9 +1077,9 @@ def main():
     ap.add_argument("--design", default="", metavar="SIZES",
                     help="instead of the headline workload: Tidelorn beside the Llama-family model at equal layer shape, "
                          "comma-separated sizes of " + "/".join(DESIGN_SIZES))
-    ap.add_argument("--design-model", default="tidelorn", choices=["tidelorn", "detatar"],
+    ap.add_argument("--design-model", default="tidelorn", choices=["tidelorn", "detatar", "tefovik"],
                     help="with --design: which design is measured (tidelorn: beside the Llama-family model; detatar: beside "
-                         "Tidelorn; sizes " + "/".join(DETATAR_SIZES) + ")")
+                         "Tidelorn; tefovik: beside Detatar; sizes " + "/".join(DETATAR_SIZES) + ")")
     args = ap.parse_args()
     if args.design:
         return run_design(args)

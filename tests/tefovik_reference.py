@@ -76,6 +76,57 @@ def softplus(z):
     return torch.where(z > 30, z, torch.log1p(torch.exp(torch.clamp(z, max=30))))
 
 
+def block_attention(q, k, v, pos_q, pos_k, scale, size):
+    """q [Tq, H, D], k [Tk, G, D], v [Tk, G, V]: softmax attention of every query over the keys chunk_mask lets it see."""
+    rep = q.shape[1] // k.shape[1]
+    k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
+    s = torch.einsum("ihd,jhd->hij", q, k) * scale
+    s = s.masked_fill(~chunk_mask(pos_q, pos_k, size)[None], -math.inf)
+    return torch.einsum("hij,jhv->ihv", torch.softmax(s, -1), v)
+
+
+def state_space_scan(x, B, C, dt, a, D, S=None):
+    """x [T, H, V], B / C [T, G, N], dt / a [T, H] (step size and decay), D [H]:  S <- a S + dt B x^T;  y = S^T C + D x.
+    Returns (y, final states [H, N, V])."""
+    T, H, V = x.shape
+    N, rep = B.shape[-1], H // B.shape[1]
+    S = x.new_zeros(H, N, V) if S is None else S.clone()
+    y = x.new_zeros(T, H, V)
+    for t in range(T):
+        for h in range(H):
+            g = h // rep
+            S[h] = a[t, h] * S[h] + dt[t, h] * torch.outer(B[t, g], x[t, h])
+            y[t, h] = S[h].T @ C[t, g] + D[h] * x[t, h]
+    return y, S
+
+
+def delta_rule_scan(q, k, v, beta, decay, S=None):
+    """q / k [T, G, D] (already normalised), v [T, H, V], beta [T, H], decay [T, H, D]:
+    S <- diag(decay) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.  Returns (o, final states [H, D, V])."""
+    T, H, V = v.shape
+    D, rep = q.shape[-1], H // q.shape[1]
+    S = v.new_zeros(H, D, V) if S is None else S.clone()
+    o = v.new_zeros(T, H, V)
+    for t in range(T):
+        for h in range(H):
+            g = h // rep
+            S[h] = decay[t, h][:, None] * S[h]
+            u = beta[t, h] * (v[t, h] - S[h].T @ k[t, g])
+            S[h] = S[h] + torch.outer(k[t, g], u)
+            o[t, h] = S[h].T @ q[t, g]
+    return o, S
+
+
+def unit_vectors(x, eps=1e-6):
+    return x / torch.sqrt((x * x).sum(-1, keepdim=True) + eps)
+
+
+def group_rms(y, parts, eps):
+    T, W = y.shape
+    y = y.view(T, parts, W // parts)
+    return (y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)).reshape(T, W)
+
+
 # ------------------------------------------------------------------------------------------------ mixers
 
 def chunked_attention(h, W, p, m, eps, pos):
@@ -91,12 +142,7 @@ def chunked_attention(h, W, p, m, eps, pos):
     q = rotate_pairs(q, pos, rot["base"], rot["dims"])
     k = rotate_pairs(k, pos, rot["base"], rot["dims"])
     v = rotate_pairs(v.view(T, G, V), pos, rot["base"], V)
-    rep = H // G
-    k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
-    s = torch.einsum("ihd,jhd->hij", q, k) * m["scale"]
-    size = (m.get("mask") or {}).get("size", 0)
-    s = s.masked_fill(~chunk_mask(pos, pos, size)[None], -math.inf)
-    o = torch.einsum("hij,jhv->ihv", torch.softmax(s, -1), v)
+    o = block_attention(q, k, v, pos, pos, m["scale"], (m.get("mask") or {}).get("size", 0))
     o = rotate_pairs(o, pos, rot["base"], V, sign=-1.0)
     o = o * torch.sigmoid(h @ W[p + "g"].T)[:, :, None]
     return o.reshape(T, H * V) @ W[p + "o"].T
@@ -110,22 +156,11 @@ def gated_delta_rule(h, W, p, m, eps):
     q = F.silu(short_conv(h @ W[p + "q"].T, W[p + "q.conv"])[0]).view(T, G, D)
     k = F.silu(short_conv(h @ W[p + "k"].T, W[p + "k.conv"])[0]).view(T, G, D)
     v = F.silu(short_conv(h @ W[p + "v"].T, W[p + "v.conv"])[0]).view(T, H, V)
-    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
-    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    q, k = unit_vectors(q) * D ** -0.5, unit_vectors(k)
     beta = torch.sigmoid(h @ W[p + "b"].T)                                            # [T, H]
     lam = torch.exp(W[p + "A_log"]).view(1, H, 1)
     decay = torch.exp(-lam * softplus((h @ W[p + "a1"].T) @ W[p + "a2"].T + W[p + "dt_bias"]).view(T, H, D))
-    rep = H // G
-    out = h.new_zeros(T, H, V)
-    for hh in range(H):
-        S = h.new_zeros(D, V)
-        kv = hh // rep
-        for t in range(T):
-            S = decay[t, hh][:, None] * S
-            u = beta[t, hh] * (v[t, hh] - S.T @ k[t, kv])
-            S = S + torch.outer(k[t, kv], u)
-            out[t, hh] = S.T @ q[t, kv]
-    out = rms_norm(out, W[p + "norm"], eps)
+    out = rms_norm(delta_rule_scan(q, k, v, beta, decay)[0], W[p + "norm"], eps)
     out = out * torch.sigmoid((h @ W[p + "g1"].T) @ W[p + "g2"].T).view(T, H, V)
     return out.reshape(T, H * V) @ W[p + "o"].T
 
@@ -148,19 +183,8 @@ def mamba2_mixer(h, W, p, m, eps):
     C = xbc[:, inner + G * N:].view(T, G, N)
     dt = softplus(dt + W[p + "dt_bias"])                                              # [T, H]
     a = torch.exp(-torch.exp(W[p + "A_log"]) * dt)
-    rep = H // G
-    y = h.new_zeros(T, H, V)
-    for hh in range(H):
-        S = h.new_zeros(N, V)
-        g = hh // rep
-        for t in range(T):
-            S = a[t, hh] * S + dt[t, hh] * torch.outer(B[t, g], x[t, hh])
-            y[t, hh] = S.T @ C[t, g] + W[p + "D"][hh] * x[t, hh]
-    y = y.reshape(T, inner) * F.silu(z)
-    parts = m.get("norm_groups", 1)
-    y = y.view(T, parts, inner // parts)
-    y = (y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)).reshape(T, inner) * W[p + "norm"]
-    return y @ W[p + "o"].T
+    y = state_space_scan(x, B, C, dt, a, W[p + "D"])[0].reshape(T, inner) * F.silu(z)
+    return group_rms(y, m.get("norm_groups", 1), eps) * W[p + "norm"] @ W[p + "o"].T
 
 
 def squared_relu_mlp(h, W, p):
