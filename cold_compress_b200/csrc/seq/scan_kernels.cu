@@ -68,12 +68,13 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 // ------------------------------------------------------------------------------------------------ norm after the sum
 // One CTA per row.  The sum is kept in shared memory so that the variance is the mean of the squared deviations from
-// the mean (two passes), not a difference of two large numbers.
+// the mean (two passes), not a difference of two large numbers.  Every pass is a chain of dependent loads, so a step
+// of few rows runs 1024 threads per row (few loads per thread) and a long one 256 (more rows per SM).
 template <typename AT>
-__global__ void __launch_bounds__(256) sum_norm_kernel(const CcSeqSumNorm a) {
+__global__ void __launch_bounds__(1024) sum_norm_kernel(const CcSeqSumNorm a) {
     extern __shared__ float sn_s[];
     __shared__ float red[32];
-    const int t = blockIdx.x, E = a.E, tid = threadIdx.x;
+    const int t = blockIdx.x, E = a.E, tid = threadIdx.x, nth = blockDim.x;
     const size_t src = a.rows != nullptr ? (size_t)a.rows[t] : (size_t)t;
     const float* x = a.x != nullptr ? a.x + src * E : nullptr;
     const float* y = a.y != nullptr ? a.y + src * a.ldy : nullptr;
@@ -81,16 +82,16 @@ __global__ void __launch_bounds__(256) sum_norm_kernel(const CcSeqSumNorm a) {
     float ry = 1.f, ry2 = 1.f;
     if (y != nullptr && a.y_norm_w != nullptr) {
         float ss = 0.f;
-        for (int e = tid; e < E; e += 256) ss = fmaf(y[e], y[e], ss);
+        for (int e = tid; e < E; e += nth) ss = fmaf(y[e], y[e], ss);
         ry = 1.0f / sqrtf(block_sum(ss, red) / (float)E + a.eps);
     }
     if (y2 != nullptr && a.y2_norm_w != nullptr) {
         float ss = 0.f;
-        for (int e = tid; e < E; e += 256) ss = fmaf(y2[e], y2[e], ss);
+        for (int e = tid; e < E; e += nth) ss = fmaf(y2[e], y2[e], ss);
         ry2 = 1.0f / sqrtf(block_sum(ss, red) / (float)E + a.eps);
     }
     float sum = 0.f;
-    for (int e = tid; e < E; e += 256) {
+    for (int e = tid; e < E; e += nth) {
         float v = x != nullptr ? a.alpha * x[e] : 0.f;
         if (y != nullptr) {
             float r = y[e] * ry;
@@ -109,13 +110,13 @@ __global__ void __launch_bounds__(256) sum_norm_kernel(const CcSeqSumNorm a) {
     }
     const float mean = a.center ? block_sum(sum, red) / (float)E : 0.f;
     float ss = 0.f;
-    for (int e = tid; e < E; e += 256) {
+    for (int e = tid; e < E; e += nth) {
         const float d = sn_s[e] - mean;
         ss = fmaf(d, d, ss);
     }
     const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)E + a.eps);
     AT* act = (AT*)a.out_act;
-    for (int e = tid; e < E; e += 256) {
+    for (int e = tid; e < E; e += nth) {
         float r = (sn_s[e] - mean) * rinv * (a.w[e] + a.gain_offset);
         const size_t o = (size_t)t * E + e;
         if (a.out != nullptr) a.out[o] = r;
@@ -242,38 +243,45 @@ __global__ void __launch_bounds__(512) ssd_scan_kernel(const CcSeqSsdScan a) {
 }
 
 // ------------------------------------------------------------------------------------------------ delta-rule scan
-// Same tiling.  Per batch, a warp per token turns the staged rows into what the recurrence reads: q and k as unit
-// vectors (q also times q_scale), their dot product, the decays exp(-exp(A_log) softplus(.)) and beta.  Per token the
-// warps decay their rows and form partial sums of S^T k and S^T q over the decayed state; after one barrier every
-// thread adds the partials in warp order, forms u = beta (v - S^T k), writes k u^T into its rows, and warp 0 stores
-// o = S^T q + (q . k) u, which is the read-out of the state after the write.
+// CTA = one head x 32 value columns, 8 warps.  A warp owns 4 columns; the 8 lanes of a column each keep CH consecutive
+// state rows in registers, so the two sums over the rows that a token needs (S^T k and S^T q over the decayed state)
+// are three shuffle steps inside the warp: no shared-memory partials and no barrier per token, the warps run
+// independently through a batch.  Per batch of TB tokens (two cp.async buffers) a warp per token turns the staged rows
+// into what the recurrence reads: q and k as unit vectors (q also times q_scale), their dot product, the decays
+// exp(-exp(A_log) softplus(.)) and beta.  Per token: decay the rows, the two sums, u = beta (v - S^T k), S += k u^T,
+// and o = S^T q + (q . k) u, which is the read-out of the state after the write.  The q / k / decay vectors lie in
+// shared memory in runs of CH with 4 floats of padding, so that the 8 lanes' 16-byte loads fall into different banks.
+constexpr int DL_PARTS = 8, DL_WARPS = 8;
+
 template <int CH, int TB>
-__global__ void __launch_bounds__(512) delta_scan_kernel(const CcSeqDeltaScan a) {
+__global__ void __launch_bounds__(DL_WARPS * 32, 2) delta_scan_kernel(const CcSeqDeltaScan a) {
     extern __shared__ float4 sm_dl4[];
     float* sm = reinterpret_cast<float*>(sm_dl4);
-    const int D = a.D, P = (D + CH - 1) / CH, Dp = P * CH;
-    const int buf_floats = TB * (3 * Dp + SCAN_J + 2);
-    float* __restrict__ part = sm + 2 * buf_floats;   // [2][2][P][32]: token parity x (k-sum, q-sum)
+    constexpr int RUN = CH + 4, Dp = DL_PARTS * RUN, NTH = DL_WARPS * 32;
+    constexpr int buf_floats = TB * (3 * Dp + SCAN_J + 2);
+    const int D = a.D;
     const int h = blockIdx.x, j0 = blockIdx.y * SCAN_J, g = h / (a.H / a.G);
-    const int tid = threadIdx.x, nth = blockDim.x, lane = tid & 31, p = tid >> 5, j = j0 + lane;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int jl = warp * 4 + (lane >> 3), p = lane & 7, j = j0 + jl;
     const int n0 = p * CH;
     float* S = a.state + (size_t)h * D * a.V;
     float st[CH];
 #pragma unroll
     for (int c = 0; c < CH; ++c) st[c] = (n0 + c < D && j < a.V) ? S[(size_t)(n0 + c) * a.V + j] : 0.f;
-    for (int idx = tid; idx < 2 * buf_floats; idx += nth) sm[idx] = 0.f;
+    for (int idx = tid; idx < 2 * buf_floats; idx += NTH) sm[idx] = 0.f;   // rows beyond D and padding stay zero
     __syncthreads();
     const float lam = expf(a.A_log[h]);
+    auto at = [](int n) { return (n / CH) * RUN + (n % CH); };
     auto fetch = [&](int tb, float* buf) {
         const int nt = min(TB, a.T - tb);
-        for (int idx = tid; idx < nt * D; idx += nth) {
-            const int t = idx / D, n = idx - t * D;
+        for (int idx = tid; idx < nt * D; idx += NTH) {
+            const int t = idx / D, n = idx - t * D, o = t * Dp + at(n);
             const size_t row = (size_t)(tb + t) * a.ldqk + (size_t)g * D + n;
-            cp_async4(buf + t * Dp + n, a.q + row);
-            cp_async4(buf + TB * Dp + t * Dp + n, a.k + row);
-            cp_async4(buf + 2 * TB * Dp + t * Dp + n, a.a_raw + (size_t)(tb + t) * a.lda + (size_t)h * D + n);
+            cp_async4(buf + o, a.q + row);
+            cp_async4(buf + TB * Dp + o, a.k + row);
+            cp_async4(buf + 2 * TB * Dp + o, a.a_raw + (size_t)(tb + t) * a.lda + (size_t)h * D + n);
         }
-        for (int idx = tid; idx < nt * SCAN_J; idx += nth) {
+        for (int idx = tid; idx < nt * SCAN_J; idx += NTH) {
             const int t = idx / SCAN_J, c = idx - t * SCAN_J;
             if (j0 + c < a.V) cp_async4(buf + 3 * TB * Dp + idx, a.v + (size_t)(tb + t) * a.ldv + (size_t)h * a.V + j0 + c);
         }
@@ -290,48 +298,53 @@ __global__ void __launch_bounds__(512) delta_scan_kernel(const CcSeqDeltaScan a)
         __syncthreads();
         float* betas = buf + 3 * TB * Dp + TB * SCAN_J;
         float* qks = betas + TB;
-        for (int t = p; t < nt; t += P) {     // a warp per token
+        for (int t = warp; t < nt; t += DL_WARPS) {     // a warp per token
             float* q = buf + t * Dp;
             float* k = buf + TB * Dp + t * Dp;
             float* gd = buf + 2 * TB * Dp + t * Dp;
             float sq = 0.f, sk = 0.f;
-            for (int n = lane; n < D; n += 32) { sq = fmaf(q[n], q[n], sq); sk = fmaf(k[n], k[n], sk); }
+            for (int n = lane; n < D; n += 32) { const int o = at(n); sq = fmaf(q[o], q[o], sq); sk = fmaf(k[o], k[o], sk); }
             const float rq = a.q_scale / sqrtf(warp_sum(sq) + a.unit_eps), rk = 1.0f / sqrtf(warp_sum(sk) + a.unit_eps);
             float dot = 0.f;
             for (int n = lane; n < D; n += 32) {
-                const float qn = q[n] * rq, kn = k[n] * rk;
-                q[n] = qn;
-                k[n] = kn;
+                const int o = at(n);
+                const float qn = q[o] * rq, kn = k[o] * rk;
+                q[o] = qn;
+                k[o] = kn;
                 dot = fmaf(qn, kn, dot);
-                gd[n] = expf(-lam * softplusf_(gd[n] + a.dt_bias[(size_t)h * D + n]));
+                gd[o] = expf(-lam * softplusf_(gd[o] + a.dt_bias[(size_t)h * D + n]));
             }
             dot = warp_sum(dot);
             if (lane == 0) { qks[t] = dot; betas[t] = sigmoidf_(betas[t]); }
         }
         __syncthreads();
-        const float* __restrict__ qs = buf + n0;
-        const float* __restrict__ ks = buf + TB * Dp + n0;
-        const float* __restrict__ gs = buf + 2 * TB * Dp + n0;
+        const float4* __restrict__ q4 = reinterpret_cast<const float4*>(buf + p * RUN);
+        const float4* __restrict__ k4 = reinterpret_cast<const float4*>(buf + TB * Dp + p * RUN);
+        const float4* __restrict__ g4 = reinterpret_cast<const float4*>(buf + 2 * TB * Dp + p * RUN);
         const float* __restrict__ vs = buf + 3 * TB * Dp;
+        float* orow = a.o + (size_t)tb * a.H * a.V + (size_t)h * a.V + j;
         for (int t = 0; t < nt; ++t) {
-            float* pk = part + ((tb + t) & 1) * 2 * P * SCAN_J;
-            float* pq = pk + P * SCAN_J;
-            float rk = 0.f, rq = 0.f;
+            float kk[CH];
+            float rk0 = 0.f, rk1 = 0.f, rq0 = 0.f, rq1 = 0.f;
 #pragma unroll
-            for (int c = 0; c < CH; ++c) {
-                st[c] *= gs[t * Dp + c];
-                rk = fmaf(ks[t * Dp + c], st[c], rk);
-                rq = fmaf(qs[t * Dp + c], st[c], rq);
+            for (int c4 = 0; c4 < CH / 4; ++c4) {
+                const float4 gv = g4[t * (Dp / 4) + c4], kv = k4[t * (Dp / 4) + c4], qv = q4[t * (Dp / 4) + c4];
+                kk[4 * c4] = kv.x; kk[4 * c4 + 1] = kv.y; kk[4 * c4 + 2] = kv.z; kk[4 * c4 + 3] = kv.w;
+                st[4 * c4] *= gv.x;     rk0 = fmaf(kv.x, st[4 * c4], rk0);     rq0 = fmaf(qv.x, st[4 * c4], rq0);
+                st[4 * c4 + 1] *= gv.y; rk1 = fmaf(kv.y, st[4 * c4 + 1], rk1); rq1 = fmaf(qv.y, st[4 * c4 + 1], rq1);
+                st[4 * c4 + 2] *= gv.z; rk0 = fmaf(kv.z, st[4 * c4 + 2], rk0); rq0 = fmaf(qv.z, st[4 * c4 + 2], rq0);
+                st[4 * c4 + 3] *= gv.w; rk1 = fmaf(kv.w, st[4 * c4 + 3], rk1); rq1 = fmaf(qv.w, st[4 * c4 + 3], rq1);
             }
-            pk[p * SCAN_J + lane] = rk;
-            pq[p * SCAN_J + lane] = rq;
-            __syncthreads();
-            float sk = 0.f, sq = 0.f;
-            for (int w = 0; w < P; ++w) { sk += pk[w * SCAN_J + lane]; sq += pq[w * SCAN_J + lane]; }
-            const float u = betas[t] * (vs[t * SCAN_J + lane] - sk);
+            float rk = rk0 + rk1, rq = rq0 + rq1;
 #pragma unroll
-            for (int c = 0; c < CH; ++c) st[c] = fmaf(ks[t * Dp + c], u, st[c]);
-            if (p == 0 && j < a.V) a.o[(size_t)(tb + t) * a.H * a.V + (size_t)h * a.V + j] = fmaf(qks[t], u, sq);
+            for (int o = 1; o < DL_PARTS; o <<= 1) {
+                rk += __shfl_xor_sync(0xffffffffu, rk, o);
+                rq += __shfl_xor_sync(0xffffffffu, rq, o);
+            }
+            const float u = betas[t] * (vs[t * SCAN_J + jl] - rk);
+#pragma unroll
+            for (int c = 0; c < CH; ++c) st[c] = fmaf(kk[c], u, st[c]);
+            if (p == 0 && j < a.V) orow[(size_t)t * a.H * a.V] = fmaf(qks[t], u, rq);
         }
         __syncthreads();   // the batch's buffer is free for the fetch after next
     }
@@ -361,6 +374,33 @@ __global__ void gated_rms_groups_kernel(const float* __restrict__ y, const float
     }
     const float rinv = 1.0f / sqrtf(warp_sum(ss) / (float)Wg + eps);
     for (int e = lane; e < Wg; e += 32) {
+        float v = row[e];
+        const float ga = grow != nullptr ? unit_act(grow[e], gate_act) : 1.f;
+        if (pre) v *= ga;
+        v = v * rinv * w[(base + e) % w_len];
+        if (!pre) v *= ga;
+        stf(out, t * W + base + e, v);
+    }
+}
+
+// The same with a CTA per (token, group), for wide groups.
+template <typename OT>
+__global__ void __launch_bounds__(1024) gated_rms_groups_wide_kernel(const float* __restrict__ y, const float* __restrict__ gate, int64_t ldg,
+                                                                      int gate_act, int gate_first, const float* __restrict__ w, int w_len,
+                                                                      OT* __restrict__ out, int W, int groups, float eps) {
+    __shared__ float red[32];
+    const size_t t = blockIdx.x;
+    const int grp = blockIdx.y, Wg = W / groups, base = grp * Wg, tid = threadIdx.x, nth = blockDim.x;
+    const float* row = y + t * W + base;
+    const float* grow = gate != nullptr ? gate + t * ldg + base : nullptr;
+    const bool pre = grow != nullptr && gate_first;
+    float ss = 0.f;
+    for (int e = tid; e < Wg; e += nth) {
+        const float v = pre ? row[e] * unit_act(grow[e], gate_act) : row[e];
+        ss = fmaf(v, v, ss);
+    }
+    const float rinv = 1.0f / sqrtf(block_sum(ss, red) / (float)Wg + eps);
+    for (int e = tid; e < Wg; e += nth) {
         float v = row[e];
         const float ga = grow != nullptr ? unit_act(grow[e], gate_act) : 1.f;
         if (pre) v *= ga;
@@ -486,12 +526,11 @@ static int launch_ssd(const CcSeqSsdScan* a, cudaStream_t st) {
 
 template <int CH, int TB>
 static int launch_delta(const CcSeqDeltaScan* a, cudaStream_t st) {
-    const int P = (a->D + CH - 1) / CH;
-    const size_t smem = sizeof(float) * (2 * (size_t)TB * (3 * P * CH + SCAN_J + 2) + 4 * (size_t)P * SCAN_J);
+    const size_t smem = sizeof(float) * 2 * (size_t)TB * (3 * DL_PARTS * (CH + 4) + SCAN_J + 2);
     static size_t configured = 48 * 1024;
     if (int rc = set_smem(delta_scan_kernel<CH, TB>, smem, configured)) return rc;
     dim3 grid(a->H, (a->V + SCAN_J - 1) / SCAN_J);
-    delta_scan_kernel<CH, TB><<<grid, P * 32, smem, st>>>(*a);
+    delta_scan_kernel<CH, TB><<<grid, DL_WARPS * 32, smem, st>>>(*a);
     return cuda_check("delta_scan_kernel");
 }
 
@@ -516,11 +555,12 @@ int cc_seq_sum_norm(const CcSeqSumNorm* a, void* stream) {
     const size_t smem = sizeof(float) * (size_t)a->E;
     if (smem > 200 * 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "sum_norm: rows longer than 51200");
     cudaStream_t st = (cudaStream_t)stream;
+    const int threads = a->T < 64 ? (a->E >= 1024 ? 1024 : ((a->E + 31) / 32) * 32) : 256;
 #define CALL(AT)                                                                 \
     {                                                                            \
         static size_t configured = 48 * 1024;                                    \
         if (int rc = set_smem(sum_norm_kernel<AT>, smem, configured)) return rc; \
-        sum_norm_kernel<AT><<<a->T, 256, smem, st>>>(*a);                        \
+        sum_norm_kernel<AT><<<a->T, threads, smem, st>>>(*a);                    \
     }
     CCN_ST(a->out_act ? a->act_dtype : CC_DT_F32, CALL);
 #undef CALL
@@ -555,8 +595,9 @@ int cc_seq_delta_scan(const CcSeqDeltaScan* a, void* stream) {
         return fail(CC_SEQ_ERR_INVALID_ARG, "delta_scan: bad argument");
     if (a->D > 256) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "delta_scan: key heads wider than 256");
     cudaStream_t st = (cudaStream_t)stream;
-    if (a->D <= 128) return launch_delta<8, 16>(a, st);
-    return launch_delta<16, 8>(a, st);
+    if (a->D <= 64) return launch_delta<8, 16>(a, st);      // rows per lane: 8 lanes share a column's rows
+    if (a->D <= 128) return launch_delta<16, 16>(a, st);
+    return launch_delta<32, 16>(a, st);
 }
 
 int cc_seq_gated_rms_groups(const float* y, const float* gate, int64_t ldg, int32_t gate_act, int32_t gate_first,
@@ -567,6 +608,16 @@ int cc_seq_gated_rms_groups(const float* y, const float* gate, int64_t ldg, int3
     cudaStream_t st = (cudaStream_t)stream;
     const size_t warps = (size_t)T * groups;
     const unsigned blocks = (unsigned)((warps + 7) / 8);
+    const int Wg = W / groups;
+    if (Wg >= 512 && groups <= 65535) {     // wide groups: a CTA each, 4 elements per thread when the step has few rows
+        const int per = T < 64 ? 4 : 16;
+        int threads = ((Wg + per - 1) / per + 31) / 32 * 32;
+        threads = threads > 1024 ? 1024 : threads;
+#define CALL(OT) gated_rms_groups_wide_kernel<OT><<<dim3(T, groups), threads, 0, st>>>(y, gate, ldg, gate_act, gate_first, w, w_len, (OT*)out, W, groups, eps)
+        CCN_ST(out_dtype, CALL);
+#undef CALL
+        return cuda_check("gated_rms_groups_wide_kernel");
+    }
 #define CALL(OT) gated_rms_groups_kernel<OT><<<blocks, 256, 0, st>>>(y, gate, ldg, gate_act, gate_first, w, w_len, (OT*)out, T, W, groups, eps)
     CCN_ST(out_dtype, CALL);
 #undef CALL
