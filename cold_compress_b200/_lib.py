@@ -260,7 +260,7 @@ class CcSeqSsdScan(C.Structure):
 class CcSeqDeltaScan(C.Structure):
     _fields_ = [("q", _vp), ("k", _vp), ("ldqk", _i64), ("v", _vp), ("ldv", _i64), ("beta_raw", _vp), ("ldb", _i64),
                 ("a_raw", _vp), ("lda", _i64), ("dt_bias", _vp), ("A_log", _vp), ("state", _vp), ("o", _vp)] + [
-        (n, _i32) for n in ("T", "H", "G", "D", "V")] + [("q_scale", _f32), ("unit_eps", _f32)]
+        (n, _i32) for n in ("T", "H", "G", "D", "V")] + [("q_scale", _f32), ("unit_eps", _f32), ("qk", _vp), ("prepared", _i32)]
 
 
 class CcSeqQkvRope(C.Structure):
@@ -274,6 +274,7 @@ SEQ_EXPORTS.update({
     "cc_seq_short_conv": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp]),
     "cc_seq_ssd_scan": (C.c_int, [C.POINTER(CcSeqSsdScan), _vp]),
     "cc_seq_delta_scan": (C.c_int, [C.POINTER(CcSeqDeltaScan), _vp]),
+    "cc_seq_delta_prepare": (C.c_int, [C.POINTER(CcSeqDeltaScan), _vp, _vp, _vp, _vp, _vp, _vp]),
     "cc_seq_gated_rms_groups": (C.c_int, [_vp, _vp, _i64, _i32, _i32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _f32, _vp]),
     "cc_seq_qkv_rope": (C.c_int, [C.POINTER(CcSeqQkvRope), _vp]),
     "cc_seq_turn_heads_gate": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _f32, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _vp]),

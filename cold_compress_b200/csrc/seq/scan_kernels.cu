@@ -247,11 +247,52 @@ __global__ void __launch_bounds__(512) ssd_scan_kernel(const CcSeqSsdScan a) {
 // state rows in registers, so the two sums over the rows that a token needs (S^T k and S^T q over the decayed state)
 // are three shuffle steps inside the warp: no shared-memory partials and no barrier per token, the warps run
 // independently through a batch.  Per batch of TB tokens (two cp.async buffers) a warp per token turns the staged rows
-// into what the recurrence reads: q and k as unit vectors (q also times q_scale), their dot product, the decays
+// (unless a separate launch has prepared them: a.prepared) into what the recurrence reads: q and k as unit vectors (q also times q_scale), their dot product, the decays
 // exp(-exp(A_log) softplus(.)) and beta.  Per token: decay the rows, the two sums, u = beta (v - S^T k), S += k u^T,
 // and o = S^T q + (q . k) u, which is the read-out of the state after the write.  The q / k / decay vectors lie in
 // shared memory in runs of CH with 4 floats of padding, so that the 8 lanes' 16-byte loads fall into different banks.
 constexpr int DL_PARTS = 8, DL_WARPS = 8;
+
+// One token's rows turned into what the recurrence reads, by one warp: q and k as unit vectors (q times q_scale), the
+// decays, and (returned) q . k.  The same code serves the scan's own batches and the separate launch that long steps
+// use, so both give the same bits.
+template <typename LQ, typename LK, typename LA, typename SQ, typename SK, typename SG>
+__device__ __forceinline__ float delta_prepare_rows(int D, int lane, float q_scale, float unit_eps, float lam,
+                                                    const float* __restrict__ dt_bias, LQ ldq, LK ldk, LA lda, SQ stq, SK stk, SG stg) {
+    float sq = 0.f, sk = 0.f;
+    for (int n = lane; n < D; n += 32) { const float qv = ldq(n), kv = ldk(n); sq = fmaf(qv, qv, sq); sk = fmaf(kv, kv, sk); }
+    const float rq = q_scale / sqrtf(warp_sum(sq) + unit_eps), rk = 1.0f / sqrtf(warp_sum(sk) + unit_eps);
+    float dot = 0.f;
+    for (int n = lane; n < D; n += 32) {
+        const float qn = ldq(n) * rq, kn = ldk(n) * rk;
+        stq(n, qn);
+        stk(n, kn);
+        dot = fmaf(qn, kn, dot);
+        stg(n, expf(-lam * softplusf_(lda(n) + dt_bias[n])));
+    }
+    return warp_sum(dot);
+}
+
+// The preparation alone, a warp per (token, head), for steps long enough that it pays to spread it over the GPU
+// instead of repeating it in every column tile of the scan: qn, kn, gd [T, H * D], beta, qk [T, H].
+__global__ void delta_prepare_kernel(const CcSeqDeltaScan a, float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ gd,
+                                     float* __restrict__ beta, float* __restrict__ qk) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t th = (size_t)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (th >= (size_t)a.T * a.H) return;
+    const size_t t = th / a.H;
+    const int h = (int)(th - t * a.H), g = h / (a.H / a.G), D = a.D;
+    const float* q = a.q + t * a.ldqk + (size_t)g * D;
+    const float* k = a.k + t * a.ldqk + (size_t)g * D;
+    const float* ar = a.a_raw + t * a.lda + (size_t)h * D;
+    float* qo = qn + th * D;
+    float* ko = kn + th * D;
+    float* go = gd + th * D;
+    const float dot = delta_prepare_rows(D, lane, a.q_scale, a.unit_eps, expf(a.A_log[h]), a.dt_bias + (size_t)h * D,
+                                         [&](int n) { return q[n]; }, [&](int n) { return k[n]; }, [&](int n) { return ar[n]; },
+                                         [&](int n, float v) { qo[n] = v; }, [&](int n, float v) { ko[n] = v; }, [&](int n, float v) { go[n] = v; });
+    if (lane == 0) { qk[th] = dot; beta[th] = sigmoidf_(a.beta_raw[t * a.ldb + h]); }
+}
 
 template <int CH, int TB>
 __global__ void __launch_bounds__(DL_WARPS * 32, 2) delta_scan_kernel(const CcSeqDeltaScan a) {
@@ -274,18 +315,25 @@ __global__ void __launch_bounds__(DL_WARPS * 32, 2) delta_scan_kernel(const CcSe
     auto at = [](int n) { return (n / CH) * RUN + (n % CH); };
     auto fetch = [&](int tb, float* buf) {
         const int nt = min(TB, a.T - tb);
-        for (int idx = tid; idx < nt * D; idx += NTH) {
-            const int t = idx / D, n = idx - t * D, o = t * Dp + at(n);
-            const size_t row = (size_t)(tb + t) * a.ldqk + (size_t)g * D + n;
-            cp_async4(buf + o, a.q + row);
-            cp_async4(buf + TB * Dp + o, a.k + row);
-            cp_async4(buf + 2 * TB * Dp + o, a.a_raw + (size_t)(tb + t) * a.lda + (size_t)h * D + n);
-        }
+        // thread -> (token lane, channel): no division per copy
+        const int lanes_t = D <= NTH / 2 ? NTH / ((D + 31) / 32 * 32) : 1, width = NTH / lanes_t;
+        const int t0 = tid / width, nb = tid - t0 * width;
+        for (int t = t0; t < nt; t += lanes_t)
+            for (int n = nb; n < D; n += width) {
+                const int o = t * Dp + at(n);
+                const size_t row = (size_t)(tb + t) * a.ldqk + (size_t)g * D + n;
+                cp_async4(buf + o, a.q + row);
+                cp_async4(buf + TB * Dp + o, a.k + row);
+                cp_async4(buf + 2 * TB * Dp + o, a.a_raw + (size_t)(tb + t) * a.lda + (size_t)h * D + n);
+            }
         for (int idx = tid; idx < nt * SCAN_J; idx += NTH) {
             const int t = idx / SCAN_J, c = idx - t * SCAN_J;
             if (j0 + c < a.V) cp_async4(buf + 3 * TB * Dp + idx, a.v + (size_t)(tb + t) * a.ldv + (size_t)h * a.V + j0 + c);
         }
-        if (tid < nt) cp_async4(buf + 3 * TB * Dp + TB * SCAN_J + tid, a.beta_raw + (size_t)(tb + tid) * a.ldb + h);
+        if (tid < nt) {
+            cp_async4(buf + 3 * TB * Dp + TB * SCAN_J + tid, a.beta_raw + (size_t)(tb + tid) * a.ldb + h);
+            if (a.prepared) cp_async4(buf + 3 * TB * Dp + TB * SCAN_J + TB + tid, a.qk + (size_t)(tb + tid) * a.H + h);
+        }
         cp_async_commit();
     };
     fetch(0, sm);
@@ -298,31 +346,25 @@ __global__ void __launch_bounds__(DL_WARPS * 32, 2) delta_scan_kernel(const CcSe
         __syncthreads();
         float* betas = buf + 3 * TB * Dp + TB * SCAN_J;
         float* qks = betas + TB;
-        for (int t = warp; t < nt; t += DL_WARPS) {     // a warp per token
-            float* q = buf + t * Dp;
-            float* k = buf + TB * Dp + t * Dp;
-            float* gd = buf + 2 * TB * Dp + t * Dp;
-            float sq = 0.f, sk = 0.f;
-            for (int n = lane; n < D; n += 32) { const int o = at(n); sq = fmaf(q[o], q[o], sq); sk = fmaf(k[o], k[o], sk); }
-            const float rq = a.q_scale / sqrtf(warp_sum(sq) + a.unit_eps), rk = 1.0f / sqrtf(warp_sum(sk) + a.unit_eps);
-            float dot = 0.f;
-            for (int n = lane; n < D; n += 32) {
-                const int o = at(n);
-                const float qn = q[o] * rq, kn = k[o] * rk;
-                q[o] = qn;
-                k[o] = kn;
-                dot = fmaf(qn, kn, dot);
-                gd[o] = expf(-lam * softplusf_(gd[o] + a.dt_bias[(size_t)h * D + n]));
+        if (!a.prepared) {
+            for (int t = warp; t < nt; t += DL_WARPS) {     // a warp per token
+                float* q = buf + t * Dp;
+                float* k = buf + TB * Dp + t * Dp;
+                float* gd = buf + 2 * TB * Dp + t * Dp;
+                const float dot = delta_prepare_rows(D, lane, a.q_scale, a.unit_eps, lam, a.dt_bias + (size_t)h * D,
+                                                     [&](int n) { return q[at(n)]; }, [&](int n) { return k[at(n)]; }, [&](int n) { return gd[at(n)]; },
+                                                     [&](int n, float v) { q[at(n)] = v; }, [&](int n, float v) { k[at(n)] = v; },
+                                                     [&](int n, float v) { gd[at(n)] = v; });
+                if (lane == 0) { qks[t] = dot; betas[t] = sigmoidf_(betas[t]); }
             }
-            dot = warp_sum(dot);
-            if (lane == 0) { qks[t] = dot; betas[t] = sigmoidf_(betas[t]); }
+            __syncthreads();
         }
-        __syncthreads();
         const float4* __restrict__ q4 = reinterpret_cast<const float4*>(buf + p * RUN);
         const float4* __restrict__ k4 = reinterpret_cast<const float4*>(buf + TB * Dp + p * RUN);
         const float4* __restrict__ g4 = reinterpret_cast<const float4*>(buf + 2 * TB * Dp + p * RUN);
         const float* __restrict__ vs = buf + 3 * TB * Dp;
         float* orow = a.o + (size_t)tb * a.H * a.V + (size_t)h * a.V + j;
+#pragma unroll 2
         for (int t = 0; t < nt; ++t) {
             float kk[CH];
             float rk0 = 0.f, rk1 = 0.f, rq0 = 0.f, rq1 = 0.f;
@@ -589,9 +631,18 @@ int cc_seq_ssd_scan(const CcSeqSsdScan* a, void* stream) {
     return launch_ssd<16, 16>(a, st);
 }
 
+int cc_seq_delta_prepare(const CcSeqDeltaScan* a, float* qn, float* kn, float* gd, float* beta, float* qk, void* stream) {
+    if (!a || !a->q || !a->k || !a->beta_raw || !a->a_raw || !a->dt_bias || !a->A_log || !qn || !kn || !gd || !beta || !qk ||
+        a->T < 1 || a->H < 1 || a->G < 1 || a->H % a->G || a->D < 1 || a->prepared)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "delta_prepare: bad argument");
+    const size_t warps = (size_t)a->T * a->H;
+    delta_prepare_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(*a, qn, kn, gd, beta, qk);
+    return cuda_check("delta_prepare_kernel");
+}
+
 int cc_seq_delta_scan(const CcSeqDeltaScan* a, void* stream) {
     if (!a || !a->q || !a->k || !a->v || !a->beta_raw || !a->a_raw || !a->dt_bias || !a->A_log || !a->state || !a->o ||
-        a->T < 1 || a->H < 1 || a->G < 1 || a->H % a->G || a->D < 1 || a->V < 1)
+        a->T < 1 || a->H < 1 || a->G < 1 || a->H % a->G || a->D < 1 || a->V < 1 || (a->prepared && (!a->qk || a->G != a->H)))
         return fail(CC_SEQ_ERR_INVALID_ARG, "delta_scan: bad argument");
     if (a->D > 256) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "delta_scan: key heads wider than 256");
     cudaStream_t st = (cudaStream_t)stream;

@@ -519,7 +519,20 @@ def delta_scan(q, k, v, beta_raw, a_raw, dt_bias, A_log, state, o, H, G, D, V, q
     a.dt_bias, a.A_log, a.state, a.o = _p(dt_bias), _p(A_log), _p(state), _p(o)
     a.T, a.H, a.G, a.D, a.V = q.shape[0], int(H), int(G), int(D), int(V)
     a.q_scale, a.unit_eps = float(q_scale), float(unit_eps)
-    _lib.check_seq(_lib.load_seq().cc_seq_delta_scan(C.byref(a), _stream()), "cc_seq_delta_scan")
+    lib = _lib.load_seq()
+    if a.T >= DELTA_PREPARE_FROM:
+        # long steps: the per-token preparation (unit vectors, decays, beta) in a launch of its own, spread over the GPU,
+        # instead of once per column tile inside the scan; same arithmetic, same bits
+        f32 = dict(dtype=torch.float32, device=o.device)
+        qn, kn, gd = (torch.empty(a.T, H * D, **f32) for _ in range(3))
+        bt, qk = torch.empty(a.T, H, **f32), torch.empty(a.T, H, **f32)
+        _lib.check_seq(lib.cc_seq_delta_prepare(C.byref(a), _p(qn), _p(kn), _p(gd), _p(bt), _p(qk), _stream()), "cc_seq_delta_prepare")
+        a.q, a.k, a.ldqk, a.a_raw, a.lda, a.beta_raw, a.ldb = _p(qn), _p(kn), H * D, _p(gd), H * D, _p(bt), H
+        a.qk, a.G, a.prepared = _p(qk), int(H), 1
+    _lib.check_seq(lib.cc_seq_delta_scan(C.byref(a), _stream()), "cc_seq_delta_scan")
+
+
+DELTA_PREPARE_FROM = 64
 
 
 def gated_rms_groups(y, gate, gate_act, gate_first, w, out, groups, eps):

@@ -395,8 +395,15 @@ typedef struct CcSeqDeltaScan {
     float* state;  float* o;
     int32_t T, H, G, D, V;
     float q_scale, unit_eps;
+    /* prepared != 0: q, k hold qn, kn per head ([T, H * D], G == H), a_raw holds the decays g, beta_raw holds beta, and
+     * qk [T, H] holds qn . kn, all as cc_seq_delta_prepare writes them; the scan then only runs the recurrence. */
+    const float* qk;
+    int32_t prepared;
 } CcSeqDeltaScan;
 int cc_seq_delta_scan(const CcSeqDeltaScan* a, void* stream);
+/* The per-token preparation of cc_seq_delta_scan alone, spread over the GPU: qn, kn, gd fp32 [T, H * D], beta, qk fp32
+ * [T, H], from an unprepared argument block.  Worth its launch for long steps; gives the same bits as the scan's own. */
+int cc_seq_delta_prepare(const CcSeqDeltaScan* a, float* qn, float* kn, float* gd, float* beta, float* qk, void* stream);
 
 /*
  * Rows y fp32 [T, W] in `groups` equal consecutive parts, each divided by its root mean square, times w[col mod
