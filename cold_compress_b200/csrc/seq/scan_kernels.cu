@@ -243,15 +243,21 @@ __global__ void __launch_bounds__(512) ssd_scan_kernel(const CcSeqSsdScan a) {
 }
 
 // ------------------------------------------------------------------------------------------------ delta-rule scan
-// CTA = one head x 32 value columns, 8 warps.  A warp owns 4 columns; the 8 lanes of a column each keep CH consecutive
-// state rows in registers, so the two sums over the rows that a token needs (S^T k and S^T q over the decayed state)
+// CTA = one head x 32 value columns.  A warp owns 4 NC columns; 8 lanes share NC columns and each keeps CH consecutive
+// state rows of them in registers, so the two sums over the rows that a token needs (S^T k and S^T q over the decayed state)
 // are three shuffle steps inside the warp: no shared-memory partials and no barrier per token, the warps run
 // independently through a batch.  Per batch of TB tokens (two cp.async buffers) a warp per token turns the staged rows
 // (unless a separate launch has prepared them: a.prepared) into what the recurrence reads: q and k as unit vectors (q also times q_scale), their dot product, the decays
 // exp(-exp(A_log) softplus(.)) and beta.  Per token: decay the rows, the two sums, u = beta (v - S^T k), S += k u^T,
 // and o = S^T q + (q . k) u, which is the read-out of the state after the write.  The q / k / decay vectors lie in
 // shared memory in runs of CH with 4 floats of padding, so that the 8 lanes' 16-byte loads fall into different banks.
-constexpr int DL_PARTS = 8, DL_WARPS = 8;
+#ifndef CC_DELTA_NC
+#define CC_DELTA_NC 1
+#endif
+// lanes per column, columns per lane.  Two columns per lane halve the shared-memory reads per column but leave half
+// as many warps to overlap the per-token chain of dependent steps: measured slower (2.04 against 1.69 ms for 4096
+// tokens of 8 heads x 128 x 128), so one column per lane is the default.
+constexpr int DL_PARTS = 8, DL_NC = CC_DELTA_NC;
 
 // One token's rows turned into what the recurrence reads, by one warp: q and k as unit vectors (q times q_scale), the
 // decays, and (returned) q . k.  The same code serves the scan's own batches and the separate launch that long steps
@@ -294,21 +300,23 @@ __global__ void delta_prepare_kernel(const CcSeqDeltaScan a, float* __restrict__
     if (lane == 0) { qk[th] = dot; beta[th] = sigmoidf_(a.beta_raw[t * a.ldb + h]); }
 }
 
-template <int CH, int TB>
-__global__ void __launch_bounds__(DL_WARPS * 32, 2) delta_scan_kernel(const CcSeqDeltaScan a) {
+template <int CH, int NC, int TB>
+__global__ void __launch_bounds__(SCAN_J / (4 * NC) * 32, 2) delta_scan_kernel(const CcSeqDeltaScan a) {
     extern __shared__ float4 sm_dl4[];
     float* sm = reinterpret_cast<float*>(sm_dl4);
-    constexpr int RUN = CH + 4, Dp = DL_PARTS * RUN, NTH = DL_WARPS * 32;
+    constexpr int NW = SCAN_J / (4 * NC), RUN = CH + 4, Dp = DL_PARTS * RUN, NTH = NW * 32;
     constexpr int buf_floats = TB * (3 * Dp + SCAN_J + 2);
     const int D = a.D;
     const int h = blockIdx.x, j0 = blockIdx.y * SCAN_J, g = h / (a.H / a.G);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int jl = warp * 4 + (lane >> 3), p = lane & 7, j = j0 + jl;
+    const int jl = (warp * 4 + (lane >> 3)) * NC, p = lane & 7, j = j0 + jl;      // this lane's first column
     const int n0 = p * CH;
     float* S = a.state + (size_t)h * D * a.V;
-    float st[CH];
+    float st[NC][CH];
 #pragma unroll
-    for (int c = 0; c < CH; ++c) st[c] = (n0 + c < D && j < a.V) ? S[(size_t)(n0 + c) * a.V + j] : 0.f;
+    for (int e = 0; e < NC; ++e)
+#pragma unroll
+        for (int c = 0; c < CH; ++c) st[e][c] = (n0 + c < D && j + e < a.V) ? S[(size_t)(n0 + c) * a.V + j + e] : 0.f;
     for (int idx = tid; idx < 2 * buf_floats; idx += NTH) sm[idx] = 0.f;   // rows beyond D and padding stay zero
     __syncthreads();
     const float lam = expf(a.A_log[h]);
@@ -347,7 +355,7 @@ __global__ void __launch_bounds__(DL_WARPS * 32, 2) delta_scan_kernel(const CcSe
         float* betas = buf + 3 * TB * Dp + TB * SCAN_J;
         float* qks = betas + TB;
         if (!a.prepared) {
-            for (int t = warp; t < nt; t += DL_WARPS) {     // a warp per token
+            for (int t = warp; t < nt; t += NW) {     // a warp per token
                 float* q = buf + t * Dp;
                 float* k = buf + TB * Dp + t * Dp;
                 float* gd = buf + 2 * TB * Dp + t * Dp;
@@ -366,33 +374,47 @@ __global__ void __launch_bounds__(DL_WARPS * 32, 2) delta_scan_kernel(const CcSe
         float* orow = a.o + (size_t)tb * a.H * a.V + (size_t)h * a.V + j;
 #pragma unroll 2
         for (int t = 0; t < nt; ++t) {
-            float kk[CH];
-            float rk0 = 0.f, rk1 = 0.f, rq0 = 0.f, rq1 = 0.f;
+            float kk[CH], rk[NC], rq[NC];
+#pragma unroll
+            for (int e = 0; e < NC; ++e) rk[e] = rq[e] = 0.f;
 #pragma unroll
             for (int c4 = 0; c4 < CH / 4; ++c4) {
                 const float4 gv = g4[t * (Dp / 4) + c4], kv = k4[t * (Dp / 4) + c4], qv = q4[t * (Dp / 4) + c4];
-                kk[4 * c4] = kv.x; kk[4 * c4 + 1] = kv.y; kk[4 * c4 + 2] = kv.z; kk[4 * c4 + 3] = kv.w;
-                st[4 * c4] *= gv.x;     rk0 = fmaf(kv.x, st[4 * c4], rk0);     rq0 = fmaf(qv.x, st[4 * c4], rq0);
-                st[4 * c4 + 1] *= gv.y; rk1 = fmaf(kv.y, st[4 * c4 + 1], rk1); rq1 = fmaf(qv.y, st[4 * c4 + 1], rq1);
-                st[4 * c4 + 2] *= gv.z; rk0 = fmaf(kv.z, st[4 * c4 + 2], rk0); rq0 = fmaf(qv.z, st[4 * c4 + 2], rq0);
-                st[4 * c4 + 3] *= gv.w; rk1 = fmaf(kv.w, st[4 * c4 + 3], rk1); rq1 = fmaf(qv.w, st[4 * c4 + 3], rq1);
-            }
-            float rk = rk0 + rk1, rq = rq0 + rq1;
+                const float g_[4] = {gv.x, gv.y, gv.z, gv.w}, k_[4] = {kv.x, kv.y, kv.z, kv.w}, q_[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
-            for (int o = 1; o < DL_PARTS; o <<= 1) {
-                rk += __shfl_xor_sync(0xffffffffu, rk, o);
-                rq += __shfl_xor_sync(0xffffffffu, rq, o);
-            }
-            const float u = betas[t] * (vs[t * SCAN_J + jl] - rk);
+                for (int i = 0; i < 4; ++i) {
+                    kk[4 * c4 + i] = k_[i];
 #pragma unroll
-            for (int c = 0; c < CH; ++c) st[c] = fmaf(kk[c], u, st[c]);
-            if (p == 0 && j < a.V) orow[(size_t)t * a.H * a.V] = fmaf(qks[t], u, rq);
+                    for (int e = 0; e < NC; ++e) {
+                        st[e][4 * c4 + i] *= g_[i];
+                        rk[e] = fmaf(k_[i], st[e][4 * c4 + i], rk[e]);
+                        rq[e] = fmaf(q_[i], st[e][4 * c4 + i], rq[e]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 1; o < DL_PARTS; o <<= 1)
+#pragma unroll
+                for (int e = 0; e < NC; ++e) {
+                    rk[e] += __shfl_xor_sync(0xffffffffu, rk[e], o);
+                    rq[e] += __shfl_xor_sync(0xffffffffu, rq[e], o);
+                }
+            const float bt = betas[t], dot = qks[t];
+#pragma unroll
+            for (int e = 0; e < NC; ++e) {
+                const float u = bt * (vs[t * SCAN_J + jl + e] - rk[e]);
+#pragma unroll
+                for (int c = 0; c < CH; ++c) st[e][c] = fmaf(kk[c], u, st[e][c]);
+                if (p == 0 && j + e < a.V) orow[(size_t)t * a.H * a.V + e] = fmaf(dot, u, rq[e]);
+            }
         }
         __syncthreads();   // the batch's buffer is free for the fetch after next
     }
 #pragma unroll
-    for (int c = 0; c < CH; ++c)
-        if (n0 + c < D && j < a.V) S[(size_t)(n0 + c) * a.V + j] = st[c];
+    for (int e = 0; e < NC; ++e)
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+            if (n0 + c < D && j + e < a.V) S[(size_t)(n0 + c) * a.V + j + e] = st[e][c];
 }
 
 // ------------------------------------------------------------------------------------------------ gated group norm
@@ -566,13 +588,13 @@ static int launch_ssd(const CcSeqSsdScan* a, cudaStream_t st) {
     return cuda_check("ssd_scan_kernel");
 }
 
-template <int CH, int TB>
+template <int CH, int NC, int TB>
 static int launch_delta(const CcSeqDeltaScan* a, cudaStream_t st) {
     const size_t smem = sizeof(float) * 2 * (size_t)TB * (3 * DL_PARTS * (CH + 4) + SCAN_J + 2);
     static size_t configured = 48 * 1024;
-    if (int rc = set_smem(delta_scan_kernel<CH, TB>, smem, configured)) return rc;
+    if (int rc = set_smem(delta_scan_kernel<CH, NC, TB>, smem, configured)) return rc;
     dim3 grid(a->H, (a->V + SCAN_J - 1) / SCAN_J);
-    delta_scan_kernel<CH, TB><<<grid, DL_WARPS * 32, smem, st>>>(*a);
+    delta_scan_kernel<CH, NC, TB><<<grid, SCAN_J / (4 * NC) * 32, smem, st>>>(*a);
     return cuda_check("delta_scan_kernel");
 }
 
@@ -646,9 +668,10 @@ int cc_seq_delta_scan(const CcSeqDeltaScan* a, void* stream) {
         return fail(CC_SEQ_ERR_INVALID_ARG, "delta_scan: bad argument");
     if (a->D > 256) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "delta_scan: key heads wider than 256");
     cudaStream_t st = (cudaStream_t)stream;
-    if (a->D <= 64) return launch_delta<8, 16>(a, st);      // rows per lane: 8 lanes share a column's rows
-    if (a->D <= 128) return launch_delta<16, 16>(a, st);
-    return launch_delta<32, 16>(a, st);
+    // rows per lane (8 lanes share a column's rows) x columns per lane
+    if (a->D <= 64) return launch_delta<8, DL_NC, 16>(a, st);
+    if (a->D <= 128) return launch_delta<16, DL_NC, 16>(a, st);
+    return launch_delta<32, DL_NC, 16>(a, st);
 }
 
 int cc_seq_gated_rms_groups(const float* y, const float* gate, int64_t ldg, int32_t gate_act, int32_t gate_first,
