@@ -753,7 +753,7 @@ def _tefovik_config(sz):
     layers = [{"type": "mamba2", "mixer": mamba, "mlp": None} if i % 2 == 0 else
               {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": {"kind": "dense", "ff": sz["ff"]}} for i in range(sz["layers"])]
     return {"architecture": "Tefovik", "vocab": sz["vocab"], "width": E, "norm": {"eps": 1e-5}, "postln_alpha": 2.0,
-            "logit_softcap": 30.0, "layers": layers}
+            "logit_softcap": 50.0, "layers": layers}
 
 
 def _tefovik_model(sz, device, dtype):

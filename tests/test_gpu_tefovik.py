@@ -133,7 +133,7 @@ def _ssd_want(x, B, C, dt_raw, dt_bias, A_log, D, H, G, N, V):
     return R.state_space_scan(d(x).view(T, H, V), d(B).view(T, G, N), d(C).view(T, G, N), dt, torch.exp(-torch.exp(d(A_log)) * dt), d(D))
 
 
-@pytest.mark.parametrize("H,G,N,V", [(1, 1, 1, 1), (4, 2, 20, 12), (3, 1, 48, 40), (2, 2, 130, 70), (6, 3, 64, 32)])
+@pytest.mark.parametrize("H,G,N,V", [(1, 1, 1, 1), (4, 2, 20, 12), (3, 1, 52, 40), (2, 2, 130, 70), (6, 3, 64, 32)])
 def test_state_space_scan_kernel_in_portions(H, G, N, V):
     ops = _ops()
     T = 45
@@ -315,8 +315,8 @@ def test_head_rows_norm_and_rotation_kernels(interleaved, H, G, Dk, Dv, dims, p0
 def test_soft_cap_kernel():
     x = torch.randn(3, 777, generator=torch.Generator().manual_seed(1)) * 40
     xd = x.to(DEV)
-    _ops().softcap(xd, 30.0)
-    _close(xd, 30.0 * torch.tanh(x.double() / 30.0), 1e-6)
+    _ops().softcap(xd, 25.0)
+    _close(xd, 25.0 * torch.tanh(x.double() / 25.0), 1e-6)
 
 
 # ----------------------------------------------------------------------------------------------- block-masked attention over the ring
@@ -340,7 +340,7 @@ def _attend(cache, q, k, v, portions, block, scale, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,Dk,Dv,block", [(6, 2, 16, 20, 9), (4, 4, 12, 8, 16), (8, 1, 48, 40, 70), (3, 1, 5, 3, 1), (17, 1, 8, 8, 33)])
+@pytest.mark.parametrize("H,G,Dk,Dv,block", [(6, 2, 16, 20, 9), (4, 4, 12, 8, 16), (10, 1, 56, 40, 70), (3, 1, 5, 3, 1), (17, 1, 8, 8, 33)])
 def test_block_masked_attention_in_portions_and_single_tokens(dtype, H, G, Dk, Dv, block):
     g = torch.Generator().manual_seed(block)
     T = 150
@@ -360,7 +360,7 @@ def test_block_masked_attention_in_portions_and_single_tokens(dtype, H, G, Dk, D
 def test_one_key_just_inside_or_outside_the_block_decides(mode, where):
     """One key's score stands far above the rest.  Inside the query's block it takes the whole softmax; one position
     earlier (the last of the block before) it must not be seen at all."""
-    block, T, Dk, Dv = 48, 48 * 5 + 20, 16, 8
+    block, T, Dk, Dv = 44, 44 * 5 + 20, 16, 8
     g = torch.Generator().manual_seed(3)
     q, k, v = torch.randn(T, 2, Dk, generator=g) * 0.1, torch.randn(T, 1, Dk, generator=g) * 0.1, torch.randn(T, 1, Dv, generator=g)
     last = T - 1
