@@ -516,7 +516,9 @@ class TefovikTransformer(nn.Module):
             param.data.copy_(value.to(param.dtype).reshape(param.shape))
 
         def conv_rows(conv: ShortConv, names, widths):
-            put(conv.weight, torch.cat([get(n, (w, conv.taps)).float() for n, w in zip(names, widths)]))
+            # a checkpoint may leave out the table of a one-tap convolution: that is the identity
+            put(conv.weight, torch.cat([get(n, (w, conv.taps)).float() if conv.taps > 1 or n in tensors else torch.ones(w, 1)
+                                        for n, w in zip(names, widths)]))
 
         cfg = self.config
         E = cfg.dim
