@@ -134,7 +134,7 @@ def check(rc: int, what: str = "") -> int:
 
 # --------------------------------------------------------------------------- libcc_b200_seq.so (include/cc_b200_seq.h)
 SEQ_SO_PATH = Path(os.environ.get("CC_B200_SEQ_LIB", PKG / "libcc_b200_seq.so"))
-SEQ_ABI_VERSION = 3
+SEQ_ABI_VERSION = 4
 DT_F32, DT_BF16 = 0, 1
 SINK_NONE, SINK_LEARNED, SINK_ZERO = 0, 1, 2
 
@@ -144,7 +144,7 @@ class CcSeqAttn(C.Structure):
                                           "input_pos", "y", "sink")] + [
         (n, C.c_int32) for n in ("T", "H", "G", "Dk", "Dv", "L", "window", "sink_mode", "cache_dtype", "y_dtype")] + [
         ("scale", C.c_float), ("append", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
-        ("block", C.c_int32)]
+        ("block", C.c_int32), ("keep_first", C.c_int32), ("softcap", C.c_float), ("dist_a", C.c_void_p), ("dist_b", C.c_void_p)]
 
 
 class CcSeqGemv(C.Structure):
@@ -197,7 +197,8 @@ class CcSeqGemvMulti(C.Structure):
 
 class CcSeqLatentPrep(C.Structure):
     _fields_ = [("inp", _vp), ("ld", _i64)] + [(n, _i32) for n in ("off_q", "q_rank", "off_kv", "kv_rank", "rot_dim", "rot_dims")] + [
-        (n, _vp) for n in ("wq", "wkv", "inv_freq", "input_pos", "cq", "krow", "vrow")] + [("dtype", _i32), ("T", _i32), ("eps", _f32)]
+        (n, _vp) for n in ("wq", "wkv", "inv_freq", "input_pos", "cq", "krow", "vrow")] + [("dtype", _i32), ("T", _i32), ("eps", _f32),
+                                                                                      ("interleaved", _i32)]
 
 
 class CcSeqLatentExpand(C.Structure):
@@ -209,7 +210,8 @@ class CcSeqLatentExpand(C.Structure):
 class CcSeqLatentDecode(C.Structure):
     _fields_ = [(n, _vp) for n in ("q", "k_new", "k_cache", "pos", "mask", "cache_cts", "input_pos", "y")] + [
         (n, _i32) for n in ("H", "Dk", "C", "L", "cache_dtype", "y_dtype")] + [("scale", _f32), ("append", _i32),
-                                                                               ("workspace", _vp), ("workspace_bytes", C.c_uint64)]
+                                                                               ("workspace", _vp), ("workspace_bytes", C.c_uint64),
+                                                                               ("sink", _vp)]
 
 
 class CcSeqWkv(C.Structure):
@@ -227,7 +229,7 @@ SEQ_EXPORTS.update({
     "cc_seq_token_shift": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _vp]),
     "cc_seq_gated_unit": (C.c_int, [_vp, _i64, _i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp]),
     "cc_seq_latent_prepare": (C.c_int, [C.POINTER(CcSeqLatentPrep), _vp]),
-    "cc_seq_rope_heads": (C.c_int, [_vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _i32, _vp]),
+    "cc_seq_rope_heads": (C.c_int, [_vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _i32, _i32, _vp]),
     "cc_seq_latent_expand": (C.c_int, [C.POINTER(CcSeqLatentExpand), _vp]),
     "cc_seq_latent_decode": (C.c_int, [C.POINTER(CcSeqLatentDecode), _vp]),
     "cc_seq_latent_decode_workspace": (C.c_uint64, [_i32, _i32, _i32]),
@@ -236,7 +238,7 @@ SEQ_EXPORTS.update({
     "cc_seq_head_gemv": (C.c_int, [_vp, _i32, _vp, _i32, _i64, _vp, _i32, _i64, _vp, _i32, _i32, _i32, _vp]),
     "cc_seq_wkv": (C.c_int, [C.POINTER(CcSeqWkv), _vp]),
     "cc_seq_head_norm_gate": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _vp]),
-    "cc_seq_moe_route": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "cc_seq_moe_route": (C.c_int, [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),
     "cc_seq_moe_group": (C.c_int, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "cc_seq_gather_rows": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "cc_seq_moe_expert_tokens": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
@@ -279,6 +281,27 @@ SEQ_EXPORTS.update({
     "cc_seq_qkv_rope": (C.c_int, [C.POINTER(CcSeqQkvRope), _vp]),
     "cc_seq_turn_heads_gate": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _f32, _vp, _i64, _vp, _i32, _i32, _i32, _i32, _vp]),
     "cc_seq_softcap": (C.c_int, [_vp, _i64, _f32, _vp]),
+})
+
+# ---- fourth part of the header: sublayers on norms of one stream, whole-row q / k norms, polynomial activation (csrc/seq/par_kernels.cu)
+PAR_MAX_OUT = 4
+
+
+class CcSeqParNorm(C.Structure):
+    _fields_ = [("x", _vp), ("a", _vp), ("lda", _i64), ("b", _vp), ("ldb", _i64), ("add", _vp), ("xhat", _vp), ("tail", _vp),
+                ("gain", _vp * PAR_MAX_OUT), ("conv_w", _vp * PAR_MAX_OUT), ("out", _vp * PAR_MAX_OUT)] + [
+        (n, _i32) for n in ("n_out", "act_dtype", "T", "E", "taps")] + [("eps", _f32)]
+
+
+class CcSeqQkRowNorm(C.Structure):
+    _fields_ = [("inp", _vp), ("ld", _i64)] + [(n, _i32) for n in ("off_q", "nq", "off_k", "nk", "off_v", "nv")] + [
+        (n, _vp) for n in ("wq", "wk", "q_out", "k_out", "v_out")] + [("out_dtype", _i32), ("T", _i32), ("eps", _f32)]
+
+
+SEQ_EXPORTS.update({
+    "cc_seq_par_norm": (C.c_int, [C.POINTER(CcSeqParNorm), _vp]),
+    "cc_seq_qk_row_norm": (C.c_int, [C.POINTER(CcSeqQkRowNorm), _vp]),
+    "cc_seq_poly_norm": (C.c_int, [_vp, _i64, _vp, _vp, _i32, _i32, _i32, _f32, _vp]),
 })
 
 _seq_lib = None

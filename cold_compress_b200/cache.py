@@ -230,27 +230,40 @@ class KVCache(nn.Module):
         None when this cache's policy does not keep a contiguous run of positions."""
         return None
 
-    def sequence_step(self, q, k_new, v_new, input_pos, y, window=0, sink=None, sink_mode=0, scale=1.0, block=0):
+    def sequence_kept(self):
+        """How many first positions own a slot for good in position-addressed steps (the others share a ring)."""
+        return 0
+
+    def sequence_step(self, q, k_new, v_new, input_pos, y, window=0, sink=None, sink_mode=0, scale=1.0, block=0,
+                      softcap=0.0, dist=None):
         """Attention of T consecutive new tokens over the cache and themselves, then their append, with every key
         addressed by position: q [T, Hq, Dk] fp32 (normalised), k_new [T, H, Dk] / v_new [T, H, Dv] in the cache's
         dtype, input_pos int32 [1] = position of the first token (device), y [T, Hq, Dv] out.  Query p sees key j
-        when j <= p and (window == 0 or p - j < window) and (block == 0 or p // block == j // block).  T == 1 is one launch (keys split over CTAs, append fused);
+        when j <= p and (window == 0 or p - j < window or j < the cache's kept first positions) and (block == 0 or
+        p // block == j // block).  A scaled score s becomes softcap * tanh(s / softcap) (softcap > 0) and then
+        s - a[h] * ln(1 + b[h] * (p - j)) (dist = (a, b), fp32 [Hq] each).  T == 1 is one launch (keys split over CTAs, append fused);
         T > 1 (and groups of more than 16 query heads) is the tiled chunk kernel followed by the append kernel.  Nothing here synchronises with the host."""
         from . import seq_ops
         keep = self.sequence_window()
         if keep is None or self.quantize:
             raise _lib.CcError(f"{type(self).__name__} cannot serve position-addressed steps")
+        kept = int(self.sequence_kept()) if window else 0
         reach = int(block) if block else int(window)      # the most positions a query looks back, 0 = without limit
         if block and window:
             raise _lib.CcError("a layer has a window or a block mask, not both")
         if (reach == 0 and keep != 0) or (reach > 0 and keep != 0 and keep < reach):
             raise _lib.CcError(f"cache keeps {keep} positions but the layer looks back {reach or 'without limit'}")
+        if self.sequence_kept() and not window:
+            raise _lib.CcError("a cache with kept first positions serves windowed layers only")
         T = q.shape[0]
         args = (q, k_new, v_new, self.k_cache, self.v_cache, self.pos, self.mask, self.cache_cts, input_pos, y, sink,
                 int(window), int(sink_mode), float(scale))
+        extra = (kept, float(softcap), None if dist is None else dist[0], None if dist is None else dist[1])
+        shaped = bool(kept or softcap or dist is not None)
         if T == 1 and q.shape[1] <= 16 * self.n_heads:   # the one-token kernel holds up to 16 query heads per KV head
-            seq_ops.seq_attention(*args, seq_ops.ATTN_DECODE_APPEND, self._sequence_workspace(q.shape[1], reach), int(block))
-        elif T == 1 and self.n_heads == 1:
+            seq_ops.seq_attention(*args, seq_ops.ATTN_DECODE_APPEND, self._sequence_workspace(q.shape[1], reach + kept if reach else 0),
+                                  int(block), *extra)
+        elif T == 1 and self.n_heads == 1 and not shaped:
             # many query heads over one shared row per position (latent rows): 16 heads per launch; every launch takes
             # the new key from k_new, the last one also appends it
             H = q.shape[1]
@@ -261,8 +274,8 @@ class KVCache(nn.Module):
                 seq_ops.seq_attention(*part, seq_ops.ATTN_DECODE_APPEND if h1 == H else seq_ops.ATTN_DECODE,
                                       self._sequence_workspace(16, reach), int(block))
         else:
-            seq_ops.seq_attention(*args, seq_ops.ATTN_CHUNK, None, int(block))
-            seq_ops.seq_attention(*args, seq_ops.ATTN_APPEND_ONLY, None, int(block))
+            seq_ops.seq_attention(*args, seq_ops.ATTN_CHUNK, None, int(block), *extra)
+            seq_ops.seq_attention(*args, seq_ops.ATTN_APPEND_ONLY, None, int(block), *extra)
         return y
 
     def _sequence_workspace(self, n_q_heads, window):
@@ -391,8 +404,12 @@ class KVCacheRecentGlobal(KVCacheHeadConstant):
     policy = _lib.POLICY_RECENT_GLOBAL
 
     def sequence_window(self):
-        # without global tokens the policy is a ring over the last L positions
-        return self.max_cache_length if not self.global_tokens else None
+        # tokens appended in order: the global tokens are the first positions and keep their slots, the policy's arg-min
+        # walks the other slots as a ring over the last L - global_tokens positions
+        return self.max_cache_length - int(self.global_tokens)
+
+    def sequence_kept(self):
+        return int(self.global_tokens)
 
 
 class KVCacheL2(KVCacheHeadSpecific):
@@ -808,9 +825,10 @@ class KVCacheLatent(KVCacheFull):
         from . import seq_ops
         seq_ops.cache_append(k_new, None, self.k_cache, None, self.pos, self.mask, self.cache_cts, input_pos)
 
-    def latent_step(self, q, k_new, input_pos, y, scale):
+    def latent_step(self, q, k_new, input_pos, y, scale, sink=None):
         """One token: q fp32 [1, H, rank + rot] over the cached rows and k_new [1, 1, rank + rot], which is then stored;
-        y [1, H, rank].  Two launches, positions read on the device (capturable in a graph)."""
+        y [1, H, rank].  `sink` (fp32 [H]): a logit per head whose exponential joins the softmax denominator.  Two
+        launches, positions read on the device (capturable in a graph)."""
         from . import seq_ops
         H, C = q.shape[-2], y.shape[-1]
         key = ("latent", H, C, self.k_cache.device)
@@ -819,7 +837,7 @@ class KVCacheLatent(KVCacheFull):
             nbytes = seq_ops.latent_decode_workspace_bytes(H, C, self.max_cache_length)
             ws = (key, torch.empty((nbytes + 3) // 4, dtype=torch.float32, device=self.k_cache.device))
             self._out["latent_ws"] = ws
-        seq_ops.latent_decode(q, k_new, self.k_cache, self.pos, self.mask, self.cache_cts, input_pos, y, scale, ws[1])
+        seq_ops.latent_decode(q, k_new, self.k_cache, self.pos, self.mask, self.cache_cts, input_pos, y, scale, ws[1], sink=sink)
         return y
 
 

@@ -65,6 +65,9 @@ def _builtin():
     if "Tefovik" not in MODEL_REGISTRY:
         from .tefovik import TefovikTransformer
         register_model("Tefovik", TefovikTransformer.from_config)
+    if "Nevodra" not in MODEL_REGISTRY:
+        from .nevodra import NevodraTransformer
+        register_model("Nevodra", NevodraTransformer.from_config)
 
 
 def is_checkpoint_folder(path) -> bool:

@@ -208,9 +208,10 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(const CcSeqLatentPr
     for (int e = tid; e < half; e += blockDim.x) {
         float sn, cs;
         sincosf(p * a.inv_freq[e], &sn, &cs);
-        const float u = tail[e], v = tail[e + half];
-        stf(kr, e, u * cs - v * sn);
-        stf(kr, e + half, v * cs + u * sn);
+        const int i0 = a.interleaved ? 2 * e : e, i1 = a.interleaved ? 2 * e + 1 : e + half;
+        const float u = tail[i0], v = tail[i1];
+        stf(kr, i0, u * cs - v * sn);
+        stf(kr, i1, v * cs + u * sn);
     }
     for (int e = 2 * half + tid; e < a.rot_dim; e += blockDim.x) stf(kr, e, tail[e]);
 }
@@ -219,7 +220,7 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(const CcSeqLatentPr
 // copied to `tail` (the absorbed query layout [H, tail_ld] at column tail_off).
 __global__ void rope_heads_kernel(float* __restrict__ q, int64_t ld, const int32_t* __restrict__ input_pos,
                                   const float* __restrict__ inv_freq, int H, int head_w, int off, int seg, int dims,
-                                  float* __restrict__ tail, int64_t tail_ld, int tail_off, int T) {
+                                  float* __restrict__ tail, int64_t tail_ld, int tail_off, int T, int interleaved) {
     const int t = blockIdx.x, half = dims / 2;
     const float p = (float)(input_pos[0] + t);
     float* row = q + (size_t)t * ld;
@@ -228,9 +229,10 @@ __global__ void rope_heads_kernel(float* __restrict__ q, int64_t ld, const int32
         float* s = row + (size_t)h * head_w + off;
         float sn, cs;
         sincosf(p * inv_freq[e], &sn, &cs);
-        const float u = s[e], v = s[e + half];
-        s[e] = u * cs - v * sn;
-        s[e + half] = v * cs + u * sn;
+        const int i0 = interleaved ? 2 * e : e, i1 = interleaved ? 2 * e + 1 : e + half;
+        const float u = s[i0], v = s[i1];
+        s[i0] = u * cs - v * sn;
+        s[i1] = v * cs + u * sn;
     }
     if (tail == nullptr) return;
     __syncthreads();
@@ -429,7 +431,8 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
 // outside the `keep` best groups (group score = its largest choice) cannot be chosen; the `top` largest choices win
 // (the lower index on a tie); weights = the winners' scores divided by their sum.
 __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ correction,
-                                 int32_t* __restrict__ ids, float* __restrict__ wts, int T, int n, int groups, int keep, int top) {
+                                 int32_t* __restrict__ ids, float* __restrict__ wts, int T, int n, int groups, int keep, int top,
+                                 int sigmoid_scores, int group_top, int renormalize, float weight_scale) {
     extern __shared__ float smr[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int t = blockIdx.x * nw + warp;
@@ -438,20 +441,43 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, c
     float* gm = c + n;
     if (t >= T) return;
     const float* z = logits + (size_t)t * ld;
-    float mx = -INFINITY;
-    for (int i = lane; i < n; i += 32) mx = fmaxf(mx, z[i]);
+    if (sigmoid_scores) {
+        for (int i = lane; i < n; i += 32) { s[i] = sigmoidf_(z[i]); c[i] = s[i] + (correction ? correction[i] : 0.f); }
+    } else {
+        float mx = -INFINITY;
+        for (int i = lane; i < n; i += 32) mx = fmaxf(mx, z[i]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float sum = 0.f;
-    for (int i = lane; i < n; i += 32) { const float e = expf(z[i] - mx); s[i] = e; sum += e; }
-    sum = warp_sum(sum);
-    for (int i = lane; i < n; i += 32) { s[i] = s[i] / sum; c[i] = s[i] + (correction ? correction[i] : 0.f); }
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+        for (int i = lane; i < n; i += 32) { const float e = expf(z[i] - mx); s[i] = e; sum += e; }
+        sum = warp_sum(sum);
+        for (int i = lane; i < n; i += 32) { s[i] = s[i] / sum; c[i] = s[i] + (correction ? correction[i] : 0.f); }
+    }
     __syncwarp();
     if (groups > 1 && keep < groups) {
         const int gs = n / groups;
         for (int g = lane; g < groups; g += 32) {
-            float m = -INFINITY;
-            for (int i = 0; i < gs; ++i) m = fmaxf(m, c[g * gs + i]);
+            float m;
+            if (group_top <= 1) {
+                m = -INFINITY;
+                for (int i = 0; i < gs; ++i) m = fmaxf(m, c[g * gs + i]);
+            } else {   // the sum of the group's group_top largest choices, largest first
+                m = 0.f;
+                float last = INFINITY;
+                int last_i = -1;
+                for (int kk = 0; kk < group_top && kk < gs; ++kk) {
+                    float bv = -INFINITY;
+                    int bi = -1;
+                    for (int i = 0; i < gs; ++i) {
+                        const float v = c[g * gs + i];
+                        const bool below = v < last || (v == last && i > last_i);
+                        if (below && (bi < 0 || v > bv)) { bv = v; bi = i; }
+                    }
+                    m += bv;
+                    last = bv;
+                    last_i = bi;
+                }
+            }
             gm[g] = m;
         }
         __syncwarp();
@@ -493,7 +519,8 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, c
         __syncwarp();
     }
     __syncwarp();
-    for (int kk = lane; kk < top; kk += 32) wts[(size_t)t * top + kk] = wts[(size_t)t * top + kk] / (wsum + 1e-20f);
+    const float div = renormalize ? wsum + 1e-20f : 1.f;
+    for (int kk = lane; kk < top; kk += 32) wts[(size_t)t * top + kk] = wts[(size_t)t * top + kk] / div * weight_scale;
 }
 
 // Groups the (token, choice) pairs of the real experts by expert: counts[e], and for every pair its row `slot` in the
@@ -575,7 +602,7 @@ __global__ void moe_combine_kernel(const CcSeqMoeCombine a) {
         for (int k = 0; k < a.top; ++k) {
             const size_t m = (size_t)t * a.top + k;
             const float w = a.wts[m];
-            if (a.ids[m] >= a.n_real) acc += w * a.h[(size_t)t * E + e];
+            if (a.ids[m] >= a.n_real) acc += a.h != nullptr ? w * a.h[(size_t)t * E + e] : 0.f;
             else acc += w * a.y[(size_t)(a.slot ? a.slot[m] : (int)m) * E + e];
         }
         if (a.shared != nullptr) {
@@ -733,6 +760,7 @@ __global__ void __launch_bounds__(LC_WARPS * 32) latent_combine_kernel(const CcS
     mx = red[0];
 #pragma unroll
     for (int i = 1; i < LC_WARPS; ++i) mx = fmaxf(mx, red[i]);
+    if (a.sink != nullptr) mx = fmaxf(mx, a.sink[h]);   // the sink: a term of the denominator without key or value
     float l = 0.f, acc[NC];
 #pragma unroll
     for (int i = 0; i < NC; ++i) acc[i] = 0.f;
@@ -751,7 +779,7 @@ __global__ void __launch_bounds__(LC_WARPS * 32) latent_combine_kernel(const CcS
     for (int i = 0; i < NC; ++i)
         if (lane + 32 * i < C) out[lane + 32 * i] = acc[i];
     __syncthreads();
-    float lt = 0.f;
+    float lt = a.sink != nullptr ? expf(a.sink[h] - mx) : 0.f;
     for (int i = 0; i < LC_WARPS; ++i) lt += smc[i * (C + 1) + C];
     for (int c = tid; c < C; c += LC_WARPS * 32) {
         float v = 0.f;
@@ -971,12 +999,12 @@ int cc_seq_latent_prepare(const CcSeqLatentPrep* a, void* stream) {
 
 int cc_seq_rope_heads(float* q, int64_t ld, const int32_t* input_pos, const float* inv_freq, int32_t T, int32_t H,
                       int32_t head_w, int32_t off, int32_t seg, int32_t dims, float* tail, int64_t tail_ld,
-                      int32_t tail_off, void* stream) {
+                      int32_t tail_off, int32_t interleaved, void* stream) {
     if (!q || !input_pos || T < 1 || H < 1 || dims < 0 || (dims & 1) || dims > seg || off + seg > head_w ||
         (dims && !inv_freq))
         return fail(CC_SEQ_ERR_INVALID_ARG, "rope_heads: bad argument");
     rope_heads_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(q, ld, input_pos, inv_freq, H, head_w, off, seg, dims, tail,
-                                                           tail_ld, tail_off, T);
+                                                           tail_ld, tail_off, T, interleaved);
     return cuda_check("rope_heads_kernel");
 }
 
@@ -1038,14 +1066,16 @@ int cc_seq_head_norm_gate(const float* o, const float* graw, int64_t ldg, const 
 }
 
 int cc_seq_moe_route(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* wts, int32_t T,
-                     int32_t n, int32_t groups, int32_t keep, int32_t top, void* stream) {
-    if (!logits || !ids || !wts || T < 1 || n < 1 || groups < 1 || n % groups || keep < 1 || top < 1 || top > n)
+                     int32_t n, int32_t groups, int32_t keep, int32_t top, int32_t sigmoid_scores, int32_t group_top,
+                     int32_t renormalize, float weight_scale, void* stream) {
+    if (!logits || !ids || !wts || T < 1 || n < 1 || groups < 1 || n % groups || keep < 1 || top < 1 || top > n || group_top < 1)
         return fail(CC_SEQ_ERR_INVALID_ARG, "moe_route: bad argument");
     const int warps = 4;
     const size_t smem = sizeof(float) * (size_t)warps * (2 * n + groups);
     if (smem > 48 * 1024) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "moe_route: too many experts");
     moe_route_kernel<<<(T + warps - 1) / warps, warps * 32, smem, (cudaStream_t)stream>>>(logits, ld, correction, ids, wts, T,
-                                                                                        n, groups, keep, top);
+                                                                                        n, groups, keep, top, sigmoid_scores,
+                                                                                        group_top, renormalize, weight_scale);
     return cuda_check("moe_route_kernel");
 }
 
@@ -1136,8 +1166,8 @@ int cc_seq_gemv_multi(const CcSeqGemvMulti* g, void* stream) {
 }
 
 int cc_seq_moe_combine(const CcSeqMoeCombine* a, void* stream) {
-    if (!a || !a->ids || !a->wts || !a->h || !a->out || a->T < 1 || a->E < 1 || a->top < 1)
-        return fail(CC_SEQ_ERR_INVALID_ARG, "moe_combine: bad argument");
+    if (!a || !a->ids || !a->wts || !a->y || !a->out || a->T < 1 || a->E < 1 || a->top < 1)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "moe_combine: bad argument");   // h may be NULL when no id reaches n_real
     moe_combine_kernel<<<a->T, 256, 0, (cudaStream_t)stream>>>(*a);
     return cuda_check("moe_combine_kernel");
 }

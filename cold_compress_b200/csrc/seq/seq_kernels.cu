@@ -123,11 +123,25 @@ __global__ void qkv_prepare_kernel(const IT* __restrict__ qkv, const float* __re
 // ------------------------------------------------------------------------------------------------ chunk attention
 constexpr int BQ = 64, BK = 32, ATT_THREADS = 256;
 
+// Slot of position j: the first keep_first positions own the first slots for good, the others share a ring over the
+// rest of the cache (keep_first == 0: slot = j mod L).
+__device__ __forceinline__ int slot_of(const CcSeqAttn& a, int j) {
+    return j < a.keep_first ? j : a.keep_first + (j - a.keep_first) % (a.L - a.keep_first);
+}
+
 __device__ __forceinline__ int key_source(const CcSeqAttn& a, int j, int p0) {
     // >= 0: cache slot, -1: not a key, <= -2: row -(s + 2) of the chunk
     if (j >= p0) return -(j - p0) - 2;
-    const int slot = j % a.L;
+    const int slot = slot_of(a, j);
     return a.pos[slot] == j ? slot : -1;
+}
+
+// What the design does to a scaled score before the softmax: a tanh soft cap, then a penalty that grows with the
+// logarithm of the distance between query i and key j, with two numbers per query head.
+__device__ __forceinline__ float shape_score(const CcSeqAttn& a, float s, int h, int dist) {
+    if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+    if (a.dist_a != nullptr) s -= a.dist_a[h] * log1pf(a.dist_b[h] * (float)dist);
+    return s;
 }
 
 // Stages `rows` rows of `width` elements (global, row r at src(r), or zeros when src(r) == nullptr) into fp32 shared
@@ -196,6 +210,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn
     float* Vs = Ks + BK * Dkp;
     float* Ss = Vs + BK * DVW;
     int* ksrc = (int*)(Ss + BQ * SP);
+    int* kpos = ksrc + BK;
 
     const int qb = blockIdx.x, h = blockIdx.y, g = h / (a.H / a.G);
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -232,10 +247,17 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn
         for (int c = 0; c < 4 * DV4; ++c) O[r][c] = 0.f;
     }
 
-    for (int jt = j_lo; jt <= j_hi; jt += BK) {
+    // the keys of this CTA in order: the kept first positions that lie below the window, then j_lo .. j_hi
+    const int kx = a.window > 0 ? min(a.keep_first, j_lo) : 0;
+    const int n_keys = kx + (j_hi - j_lo + 1);
+    for (int ut = 0; ut < n_keys; ut += BK) {
         __syncthreads();  // the previous tile is consumed
-        const int nk = min(BK, j_hi - jt + 1);
-        if (tid < BK) ksrc[tid] = tid < nk ? key_source(a, jt + tid, p0) : -1;
+        const int nk = min(BK, n_keys - ut);
+        if (tid < BK) {
+            const int u = ut + tid, j = u < kx ? u : j_lo + (u - kx);
+            kpos[tid] = j;
+            ksrc[tid] = tid < nk ? key_source(a, j, p0) : -1;
+        }
         __syncthreads();
         stage_rows<CT>(Ks, Dkp, BK, Dk, [&](int r) -> const CT* {
             const int s = ksrc[r];
@@ -278,10 +300,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_chunk_kernel(const CcSeqAttn
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const int col = tx + 16 * c;
-                const int j = jt + col;
-                const bool ok = qi < nq && col < nk && ksrc[col] != -1 && j <= i && (a.window == 0 || i - j < a.window) &&
+                const int j = kpos[col];
+                const bool ok = qi < nq && col < nk && ksrc[col] != -1 && j <= i &&
+                                (a.window == 0 || i - j < a.window || j < a.keep_first) &&
                                 (a.block == 0 || j >= (i / a.block) * a.block);
-                s[r][c] = ok ? s[r][c] * a.scale : -INFINITY;
+                s[r][c] = ok ? shape_score(a, s[r][c] * a.scale, h, i - j) : -INFINITY;
                 mx = fmaxf(mx, s[r][c]);
             }
 #pragma unroll
@@ -361,11 +384,13 @@ __host__ __device__ inline int decode_max_splits(int L, int window) {
 }
 
 // the most keys a query can see besides the limit of the cache: its window, or its block
-__host__ __device__ inline int attn_reach(const CcSeqAttn& a) { return a.block > 0 ? a.block : a.window; }
+__host__ __device__ inline int attn_reach(const CcSeqAttn& a) {
+    return a.block > 0 ? a.block : (a.window > 0 ? a.window + a.keep_first : 0);
+}
 
 template <typename CT>
 __device__ __forceinline__ void append_row(const CcSeqAttn& a, int g, int t, int p, int tid, int nthreads) {
-    const int slot = p % a.L;
+    const int slot = slot_of(a, p);
     CT* kc = (CT*)a.k_cache;
     CT* vc = (CT*)a.v_cache;
     const CT* kn = (const CT*)a.k_new;
@@ -405,7 +430,8 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_decode_kernel(const CcSeqAtt
     const int sp = blockIdx.x, g = blockIdx.y, tid = threadIdx.x;
     const int p = a.input_pos[0];
     const int j_lo = a.block > 0 ? (p / a.block) * a.block : (a.window > 0 ? max(0, p - a.window + 1) : 0);
-    const int n = p - j_lo + 1;
+    const int kx = a.window > 0 ? min(a.keep_first, j_lo) : 0;   // kept first positions below the window
+    const int n = kx + (p - j_lo + 1);
     const int n_tiles = (n + KS - 1) / KS;
     const int tiles_per = (n_tiles + DEC_MAX_SPLITS - 1) / DEC_MAX_SPLITS;
     const int nsplit = (n_tiles + tiles_per - 1) / tiles_per;
@@ -444,10 +470,11 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_decode_kernel(const CcSeqAtt
 
     const int tile_end = min(n_tiles, (sp + 1) * tiles_per);
     for (int tile = sp * tiles_per; tile < tile_end; ++tile) {
-        const int j0 = j_lo + tile * KS;
-        const int nk = min(KS, p - j0 + 1);
+        const int u0 = tile * KS;
+        const int nk = min(KS, n - u0);
         __syncthreads();   // the previous tile is consumed (first pass: qs and the running maxima are written)
-        const int src = tid < nk ? key_source(a, j0 + tid, p) : -1;
+        const int jk = u0 + tid < kx ? u0 + tid : j_lo + (u0 + tid - kx);
+        const int src = tid < nk ? key_source(a, jk, p) : -1;
         ksrc[tid] = src;
         {   // scores: one thread per key
             float acc[RMAX];
@@ -490,7 +517,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_decode_kernel(const CcSeqAtt
             }
 #pragma unroll
             for (int r = 0; r < RMAX; ++r)
-                if (r < R) Ps[r * KS + tid] = src != -1 ? acc[r] * a.scale : -INFINITY;
+                if (r < R) Ps[r * KS + tid] = src != -1 ? shape_score(a, acc[r] * a.scale, g * R + r, p - jk) : -INFINITY;
         }
         __syncthreads();
         for (int r = warp; r < R; r += DEC_THREADS / 32) {
@@ -679,7 +706,10 @@ __global__ void __launch_bounds__(DEC_THREADS) attn_decode_kernel(const CcSeqAtt
 template <typename CT>
 __global__ void cache_append_kernel(const CcSeqAttn a, int t_first) {
     const int t = t_first + blockIdx.x, g = blockIdx.y;
-    append_row<CT>(a, g, t, a.input_pos[0] + t, threadIdx.x, blockDim.x);
+    const int p = a.input_pos[0] + t;
+    // a row whose slot a later row of the same chunk takes is not written (kept first positions never are)
+    if (p >= a.keep_first && p + (a.L - a.keep_first) <= a.input_pos[0] + a.T - 1) return;
+    append_row<CT>(a, g, t, p, threadIdx.x, blockDim.x);
 }
 
 // ------------------------------------------------------------------------------------------------ post-sum norm
@@ -848,8 +878,10 @@ static int check_attn(const CcSeqAttn* a) {
     if (a->T < 1 || a->H < 1 || a->G < 1 || a->H % a->G || a->Dk < 1 || a->Dv < 1 || a->L < 1 || a->window < 0)
         return fail(CC_SEQ_ERR_INVALID_ARG, "attention: bad sizes");
     if (a->Dk > 256 || a->Dv > 256) return fail(CC_SEQ_ERR_UNSUPPORTED_SHAPE, "attention: head sizes above 256");
-    if (a->window > 0 && a->L < a->window)
-        return fail(CC_SEQ_ERR_INVALID_ARG, "attention: cache capacity below the window");
+    if (a->keep_first < 0 || (a->keep_first > 0 && a->L <= a->keep_first) || a->softcap < 0.f || (a->dist_a && !a->dist_b))
+        return fail(CC_SEQ_ERR_INVALID_ARG, "attention: bad kept-first count, soft cap or distance penalty");
+    if (a->window > 0 && a->L < a->window + a->keep_first)
+        return fail(CC_SEQ_ERR_INVALID_ARG, "attention: cache capacity below the window plus the kept first positions");
     if (a->block < 0 || (a->block > 0 && (a->window > 0 || a->L < a->block)))
         return fail(CC_SEQ_ERR_INVALID_ARG, "attention: a block mask needs a cache of at least one block and no window");
     if (a->sink_mode == CC_SINK_LEARNED && !a->sink) return fail(CC_SEQ_ERR_INVALID_ARG, "attention: sink missing");
@@ -859,7 +891,7 @@ static int check_attn(const CcSeqAttn* a) {
 template <typename CT, typename YT, int DV4>
 static int launch_chunk(const CcSeqAttn* a, cudaStream_t st) {
     const int Dkp = vec_stride(a->Dk);
-    const size_t smem = sizeof(float) * ((size_t)(BQ + BK) * Dkp + (size_t)BK * 64 * DV4 + (size_t)BQ * (BK + 4)) + sizeof(int) * BK;
+    const size_t smem = sizeof(float) * ((size_t)(BQ + BK) * Dkp + (size_t)BK * 64 * DV4 + (size_t)BQ * (BK + 4)) + sizeof(int) * 2 * BK;
     auto kern = attn_chunk_kernel<CT, YT, DV4>;
     static size_t configured = 48 * 1024;
     if (smem > configured) {
@@ -989,7 +1021,8 @@ int cc_seq_cache_append(const CcSeqAttn* a, void* stream) {
     if (!a || !a->k_new || !a->v_new || !a->k_cache || !a->v_cache || !a->pos || !a->input_pos || a->T < 1 || a->L < 1)
         return fail(CC_SEQ_ERR_INVALID_ARG, "cache_append: bad argument");
     cudaStream_t st = (cudaStream_t)stream;
-    const int t_first = a->T > a->L ? a->T - a->L : 0;
+    if (a->keep_first < 0 || a->L <= a->keep_first) return fail(CC_SEQ_ERR_INVALID_ARG, "cache_append: bad kept-first count");
+    const int t_first = (a->keep_first == 0 && a->T > a->L) ? a->T - a->L : 0;   // with kept positions every row's CTA decides
     dim3 grid(a->T - t_first, a->G);
     if (a->cache_dtype == CC_DT_F32) cache_append_kernel<float><<<grid, 64, 0, st>>>(*a, t_first);
     else if (a->cache_dtype == CC_DT_BF16) cache_append_kernel<__nv_bfloat16><<<grid, 64, 0, st>>>(*a, t_first);

@@ -193,9 +193,11 @@ class WkvMixer(nn.Module):
 
 class LatentAttention(nn.Module):
     """Causal softmax attention whose keys and values are up-projections of one cached latent per position.
-    Queries: `q = W_uq rms_norm(W_dq h)`, per head [dim unrotated | rot_dim rotated].  Keys: per head
-    `[W_uk c | rot(k_r)]` with `c = rms_norm(first kv_rank rows of W_dkv h)` and `k_r` the last rot_dim rows, shared by
-    all heads; values `W_uv c`.  Each head's output is multiplied by sigmoid of one row of `W_g h`.
+    Queries: `q = W_uq rms_norm(W_dq h)` (or, with `q_rank == 0`, one full-rank projection `q = W_q h`), per head
+    [dim unrotated | rot_dim rotated].  Keys: per head `[W_uk c | rot(k_r)]` with `c = rms_norm(first kv_rank rows of
+    W_dkv h)` and `k_r` the last rot_dim rows, shared by all heads; values `W_uv c`.  Options: `gated` multiplies each
+    head's output by sigmoid of one row of `W_g h`; `sink` adds exp of a learned logit per head to the softmax
+    denominator; `interleaved` pairs rotary dimensions (2i, 2i + 1) instead of (i, i + dims / 2).
 
     Only `[c | rot(k_r)]` is cached.  A prompt portion up-projects the cached latents of the earlier positions
     (tensor-core product) and attends over per-head rows; a single token uses the absorbed form instead: the query
@@ -203,16 +205,21 @@ class LatentAttention(nn.Module):
     the attention-weighted latent."""
 
     def __init__(self, dim: int, heads: int, head_dim: int, rot_dim: int, v_dim: int, q_rank: int, kv_rank: int,
-                 scale: float, rot_base: float, rot_dims: int, eps: float, dtype):
+                 scale: float, rot_base: float, rot_dims: int, eps: float, dtype, gated: bool = True, sink: bool = False,
+                 interleaved: bool = False):
         super().__init__()
         if rot_dims > rot_dim or rot_dims % 2:
             raise ValueError("rotary dims must be even and at most the rotated width")
         self.dim, self.heads, self.head_dim, self.rot_dim, self.v_dim = dim, heads, head_dim, rot_dim, v_dim
         self.q_rank, self.kv_rank, self.scale, self.rot_dims, self.eps = q_rank, kv_rank, float(scale), rot_dims, eps
-        self.w_in = _zeros(_pad16(q_rank + kv_rank + rot_dim + heads), dim, dtype=dtype)   # rows: dq | dkv | g | padding
-        self.q_norm = _zeros(q_rank, dtype=torch.float32)
+        self.gated, self.interleaved = bool(gated), bool(interleaved)
+        # rows of the fused input projection: query part (down-projection, or all query heads when q_rank == 0) | dkv | g | padding
+        self.q_rows = q_rank if q_rank else heads * (head_dim + rot_dim)
+        self.w_in = _zeros(_pad16(self.q_rows + kv_rank + rot_dim + (heads if gated else 0)), dim, dtype=dtype)
+        self.q_norm = _zeros(q_rank, dtype=torch.float32) if q_rank else None
         self.kv_norm = _zeros(kv_rank, dtype=torch.float32)
-        self.w_uq = _zeros(heads * (head_dim + rot_dim), q_rank, dtype=dtype)
+        self.sink = _zeros(heads, dtype=torch.float32) if sink else None
+        self.w_uq = _zeros(heads * (head_dim + rot_dim), q_rank, dtype=dtype) if q_rank else None
         self.w_ukv = _zeros(heads * (head_dim + v_dim), kv_rank, dtype=dtype)           # rows: uk (H * dim) | uv (H * vdim)
         self.w_uk_t = _zeros(heads, kv_rank, head_dim, dtype=dtype)                    # per head W_uk^T, for the absorbed query
         self.w_o = _zeros(dim, heads * v_dim, dtype=dtype)
@@ -238,20 +245,24 @@ class LatentAttention(nn.Module):
         returns the input of the output product."""
         (a,) = outs
         dev, dt = a.device, self.w_in.dtype
-        H, D, R, V, C = self.heads, self.head_dim, self.rot_dim, self.v_dim, self.kv_rank
-        cq = torch.empty(1, self.q_rank, dtype=dt, device=dev)
+        H, D, R, V, C, Q = self.heads, self.head_dim, self.rot_dim, self.v_dim, self.kv_rank, self.q_rows
+        cq = torch.empty(1, self.q_rank, dtype=dt, device=dev) if self.q_rank else None
         krow = torch.empty(1, 1, C + R, dtype=dt, device=dev)
-        seq_ops.latent_prepare(a, 0, self.q_rank, self.q_rank, C, R, self.rot_dims, self.q_norm, self.kv_norm,
-                               self.inv_freq, ip, cq, krow, None, self.eps)
-        q = _out(self.w_uq)
-        seq_ops.gemv_multi([(cq, self.w_uq, q)])
+        seq_ops.latent_prepare(a, 0, self.q_rank, Q, C, R, self.rot_dims, self.q_norm, self.kv_norm,
+                               self.inv_freq, ip, cq, krow, None, self.eps, self.interleaved)
+        if self.q_rank:
+            q = _out(self.w_uq)
+            seq_ops.gemv_multi([(cq, self.w_uq, q)])
+        else:
+            q = a[:, :Q]      # the query heads are columns of the fused projection (fp32), rotated in place
         qf = torch.empty(1, H, C + R, dtype=torch.float32, device=dev)
-        seq_ops.rope_heads(q, ip, self.inv_freq, H, D + R, D, R, self.rot_dims, tail=qf, tail_off=C)
+        seq_ops.rope_heads(q, ip, self.inv_freq, H, D + R, D, R, self.rot_dims, tail=qf, tail_off=C, interleaved=self.interleaved)
         seq_ops.head_gemv(self.w_uk_t, q, D + R, qf, C + R)
         ctx = torch.empty(1, H, C, dtype=dt, device=dev)
-        cache.latent_step(qf, krow, ip, ctx, self.scale)
+        cache.latent_step(qf, krow, ip, ctx, self.scale, sink=self.sink)
         y = torch.empty(1, H * V, dtype=dt, device=dev)
-        seq_ops.head_gemv(self.w_ukv[H * D:].view(H, V, C), ctx, C, y, V, gate=a[0, self.q_rank + C + R:self.q_rank + C + R + H])
+        seq_ops.head_gemv(self.w_ukv[H * D:].view(H, V, C), ctx, C, y, V,
+                          gate=a[0, Q + C + R:Q + C + R + H] if self.gated else None)
         return y
 
     def forward(self, hs_act: Tensor, ip: Tensor, cache, one_token_kernel: bool = True) -> Tensor:
@@ -263,16 +274,17 @@ class LatentAttention(nn.Module):
             y, out = self.finish(outs, ip, cache), _out(self.w_o)
             seq_ops.gemv_multi([(y, self.w_o, out)])
             return out
+        Q = self.q_rows
         a = _proj(hs_act, self.w_in)
-        cq = torch.empty(T, self.q_rank, dtype=dt, device=dev)
+        cq = torch.empty(T, self.q_rank, dtype=dt, device=dev) if self.q_rank else None
         krow = torch.empty(T, 1, C + R, dtype=dt, device=dev)
         lat_new = torch.empty(T, C, dtype=dt, device=dev)     # contiguous latents for the up-projection
-        seq_ops.latent_prepare(a, 0, self.q_rank, self.q_rank, C, R, self.rot_dims, self.q_norm, self.kv_norm,
-                               self.inv_freq, ip, cq, krow, lat_new, self.eps)
-        q = _proj(cq, self.w_uq)                                                        # fp32 [T, H * (D + R)]
-        gate = a[:, self.q_rank + C + R:self.q_rank + C + R + H]
+        seq_ops.latent_prepare(a, 0, self.q_rank, Q, C, R, self.rot_dims, self.q_norm, self.kv_norm,
+                               self.inv_freq, ip, cq, krow, lat_new, self.eps, self.interleaved)
+        q = _proj(cq, self.w_uq) if self.q_rank else a[:, :Q].contiguous()             # fp32 [T, H * (D + R)]
+        gate = a[:, Q + C + R:Q + C + R + H]
         p0 = int(ip.item())      # a prompt portion sizes its expanded rows on the host (one read per layer step)
-        seq_ops.rope_heads(q, ip, self.inv_freq, H, D + R, D, R, self.rot_dims)
+        seq_ops.rope_heads(q, ip, self.inv_freq, H, D + R, D, R, self.rot_dims, interleaved=self.interleaved)
         kv_new = _mm(lat_new, self.w_ukv)
         k_new = torch.empty(T, H, D + R, dtype=dt, device=dev)
         v_new = torch.empty(T, H, V, dtype=dt, device=dev)
@@ -286,9 +298,10 @@ class LatentAttention(nn.Module):
             lat_old = kv_old = k_old = v_old = pos_old = None
         seq_ops.latent_expand(kv_old, kv_new, lat_old, krow.view(T, C + R), k_old, v_old, k_new, v_new, H, D, V, R, C)
         y = torch.empty(T, H, V, dtype=dt, device=dev)
-        seq_ops.attention_rows(q.view(T, H, D + R), k_new, v_new, k_old, v_old, pos_old, ip, y, self.scale)
+        seq_ops.attention_rows(q.view(T, H, D + R), k_new, v_new, k_old, v_old, pos_old, ip, y, self.scale, sink=self.sink)
         cache.sequence_append(krow, ip)
-        seq_ops.head_gate(y, gate)
+        if self.gated:
+            seq_ops.head_gate(y, gate)
         return _proj(y.view(T, H * V), self.w_o)
 
 
@@ -320,7 +333,10 @@ class RoutedExperts(nn.Module):
     outputs form equal groups of neighbours of which only the best `keep` (by their largest choice) can be chosen; the
     `top` largest choices win and are weighted by their scores divided by their sum.  The last `identity` outputs are
     identity experts (the input itself).  A shared expert runs for every token, times sigmoid of one projection row.
-    Its router, shared-gate and shared gate/up rows are part of the layer's fused projection of h.
+    Its router, shared-gate and shared gate/up rows are part of the layer's fused projection of h.  Options: `scoring`
+    "sigmoid" scores every output on its own instead of the softmax; `group_top` makes a group's score the sum of its
+    that many largest choices instead of the largest; `renormalize=False` keeps the chosen scores as weights;
+    `weight_scale` multiplies the weights; `shared_gate=False` adds the shared expert without a gate.
 
     Steps of up to `small_t` tokens run the chosen experts through a kernel that reads the ids on the device (no host
     round trip: a decode step stays capturable); longer portions group the (token, choice) pairs by expert, read the
@@ -329,26 +345,32 @@ class RoutedExperts(nn.Module):
     small_t = 4
 
     def __init__(self, dim: int, n_experts: int, n_identity: int, ff: int, top: int, groups: int, keep: int,
-                 shared_ff: int, act: int, dtype):
+                 shared_ff: int, act: int, dtype, scoring: str = "softmax", group_top: int = 1, renormalize: bool = True,
+                 weight_scale: float = 1.0, shared_gate: bool = True):
         super().__init__()
         self.dim, self.n_real, self.n_identity, self.ff, self.top = dim, int(n_experts), int(n_identity), int(ff), int(top)
         self.groups, self.keep, self.shared_ff, self.act = int(groups), int(keep), int(shared_ff), int(act)
         if (self.n_real + self.n_identity) % self.groups:
             raise ValueError("router outputs must split into equal groups")
+        if scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"unknown router scoring {scoring!r}")
+        self.sigmoid_scores, self.group_top, self.renormalize = scoring == "sigmoid", int(group_top), bool(renormalize)
+        self.weight_scale, self.sg_rows = float(weight_scale), (1 if shared_gate and self.shared_ff else 0)
         self.correction = _zeros(self.n_real + self.n_identity, dtype=torch.float32)
         self.w_gu = _zeros(self.n_real, 2 * self.ff, dim, dtype=dtype)      # per expert: gate rows | up rows
         self.w_d = _zeros(self.n_real, dim, self.ff, dtype=dtype)
         self.w_shared_down = _zeros(dim, self.shared_ff, dtype=dtype) if self.shared_ff else None
 
     def n_rows(self):
-        return self.n_real + self.n_identity + ((1 + 2 * self.shared_ff) if self.shared_ff else 0)
+        return self.n_real + self.n_identity + ((self.sg_rows + 2 * self.shared_ff) if self.shared_ff else 0)
 
     def _route(self, hp: Tensor, off: int):
         T, dev = hp.shape[0], hp.device
         n = self.n_real + self.n_identity
         ids = torch.empty(T, self.top, dtype=torch.int32, device=dev)
         wts = torch.empty(T, self.top, dtype=torch.float32, device=dev)
-        seq_ops.moe_route(hp[:, off:off + n], self.correction, ids, wts, self.groups, self.keep, self.top)
+        seq_ops.moe_route(hp[:, off:off + n], self.correction, ids, wts, self.groups, self.keep, self.top,
+                          self.sigmoid_scores, self.group_top, self.renormalize, self.weight_scale)
         return ids, wts
 
     def _few_tokens(self, h_act: Tensor, ids: Tensor):
@@ -359,7 +381,7 @@ class RoutedExperts(nn.Module):
         return y
 
     def _combine(self, ids, wts, slot, y, h, shared, sg):
-        out = torch.empty(h.shape[0], self.dim, dtype=torch.float32, device=h.device)
+        out = torch.empty(ids.shape[0], self.dim, dtype=torch.float32, device=ids.device)
         seq_ops.moe_combine(ids, wts, slot, y, h, shared, sg, out, self.n_real)
         return out
 
@@ -370,8 +392,9 @@ class RoutedExperts(nn.Module):
         y = self._few_tokens(h_act, ids)
         jobs, shared, sg = [], None, None
         if self.shared_ff:
-            shared, sg = _out(self.w_shared_down), hp[:, off + n:off + n + 1]
-            jobs.append((hp, self.w_shared_down, shared, self.act, off + n + 1, off + n + 1 + self.shared_ff))
+            g0 = off + n + self.sg_rows
+            shared, sg = _out(self.w_shared_down), (hp[:, off + n:off + n + 1] if self.sg_rows else None)
+            jobs.append((hp, self.w_shared_down, shared, self.act, g0, g0 + self.shared_ff))
         return jobs, lambda: self._combine(ids, wts, None, y, h, shared, sg)
 
     def forward(self, hp: Tensor, off: int, h: Tensor, h_act: Tensor, one_token_kernel: bool = True) -> Tensor:
@@ -380,9 +403,10 @@ class RoutedExperts(nn.Module):
         ids, wts = self._route(hp, off)
         shared = sg = None
         if self.shared_ff:
-            sg = hp[:, off + n:off + n + 1]
+            g0 = off + n + self.sg_rows
+            sg = hp[:, off + n:off + n + 1] if self.sg_rows else None
             act = torch.empty(T, self.shared_ff, dtype=dt, device=dev)
-            seq_ops.gated_unit(hp, off + n + 1, off + n + 1 + self.shared_ff, act, self.act)
+            seq_ops.gated_unit(hp, g0, g0 + self.shared_ff, act, self.act)
             shared = _proj(act, self.w_shared_down)
         M = T * top
         if T <= self.small_t:

@@ -24,7 +24,8 @@ _library.define("seq_qkv_prepare(Tensor qkv, Tensor? bias, Tensor input_pos, Ten
                 "float gain_coef, int gain_every) -> ()")
 _library.define("seq_attention(Tensor q, Tensor k_new, Tensor v_new, Tensor(a!) k_cache, Tensor(b!) v_cache, Tensor(c!) pos, "
                 "Tensor(d!) mask, Tensor(e!) cache_cts, Tensor input_pos, Tensor(f!) y, Tensor? sink, int window, "
-                "int sink_mode, float scale, int mode, Tensor(g!)? workspace, int block=0) -> ()")
+                "int sink_mode, float scale, int mode, Tensor(g!)? workspace, int block=0, int keep_first=0, "
+                "float softcap=0.0, Tensor? dist_a=None, Tensor? dist_b=None) -> ()")
 _library.define("seq_residual_norm(Tensor(a!) x, Tensor? y, Tensor w, float alpha, float eps, Tensor(b!)? x_act) -> ()")
 _library.define("seq_clamped_glu(Tensor gu, Tensor(a!) out, float limit, float slope) -> ()")
 _library.define("seq_gemv(Tensor x, Tensor? in_norm_w, Tensor w, Tensor? bias, Tensor? res, Tensor? res_norm_w, Tensor(a!) out, "
@@ -83,12 +84,14 @@ def _seq_qkv_prepare(qkv, bias, input_pos, mix_lambda, v_first, q, k, v, H, G, D
 
 
 def _seq_attention(q, k_new, v_new, k_cache, v_cache, pos, mask, cache_cts, input_pos, y, sink, window, sink_mode, scale,
-                   mode, workspace, block=0):
+                   mode, workspace, block=0, keep_first=0, softcap=0.0, dist_a=None, dist_b=None):
     _need(("q", q, torch.float32), ("k_new", k_new, k_cache.dtype), ("v_new", v_new, k_cache.dtype), ("k_cache", k_cache, None),
           ("v_cache", v_cache, k_cache.dtype), ("pos", pos, torch.int32), ("mask", mask, torch.bool),
           ("cache_cts", cache_cts, torch.int32), ("input_pos", input_pos, torch.int32), ("y", y, None),
-          ("sink", sink, torch.float32), ("workspace", workspace, None))
+          ("sink", sink, torch.float32), ("workspace", workspace, None), ("dist_a", dist_a, torch.float32),
+          ("dist_b", dist_b, torch.float32))
     a = _lib.CcSeqAttn()
+    a.keep_first, a.softcap, a.dist_a, a.dist_b = int(keep_first), float(softcap), _p(dist_a), _p(dist_b)
     T, H, Dk = q.shape
     G, L = k_cache.shape[-3], k_cache.shape[-2]
     Dv = v_cache.shape[-1]
@@ -249,7 +252,8 @@ def gated_unit(src, off_gate, off_up, out, kind):
                                                      _stream()), "cc_seq_gated_unit")
 
 
-def latent_prepare(src, off_q, q_rank, off_kv, kv_rank, rot_dim, rot_dims, wq, wkv, inv_freq, input_pos, cq, krow, vrow, eps):
+def latent_prepare(src, off_q, q_rank, off_kv, kv_rank, rot_dim, rot_dims, wq, wkv, inv_freq, input_pos, cq, krow, vrow, eps,
+                   interleaved=False):
     _need(("wq", wq, torch.float32), ("wkv", wkv, torch.float32), ("inv_freq", inv_freq, torch.float32),
           ("input_pos", input_pos, torch.int32), ("cq", cq, krow.dtype), ("krow", krow, None), ("vrow", vrow, krow.dtype))
     a = _lib.CcSeqLatentPrep()
@@ -257,16 +261,18 @@ def latent_prepare(src, off_q, q_rank, off_kv, kv_rank, rot_dim, rot_dims, wq, w
     a.off_q, a.q_rank, a.off_kv, a.kv_rank, a.rot_dim, a.rot_dims = int(off_q), int(q_rank), int(off_kv), int(kv_rank), int(rot_dim), int(rot_dims)
     a.wq, a.wkv, a.inv_freq, a.input_pos = _p(wq), _p(wkv), _p(inv_freq), _p(input_pos)
     a.cq, a.krow, a.vrow, a.dtype, a.T, a.eps = _p(cq), _p(krow), _p(vrow), _dt(krow), src.shape[0], float(eps)
+    a.interleaved = int(bool(interleaved))
     _lib.check_seq(_lib.load_seq().cc_seq_latent_prepare(C.byref(a), _stream()), "cc_seq_latent_prepare")
 
 
-def rope_heads(q, input_pos, inv_freq, H, head_w, off, seg, dims, tail=None, tail_off=0):
-    """Rotates the segment [off, off + seg) of each of the H heads of q (fp32 [T, >= H * head_w]) in place."""
+def rope_heads(q, input_pos, inv_freq, H, head_w, off, seg, dims, tail=None, tail_off=0, interleaved=False):
+    """Rotates the segment [off, off + seg) of each of the H heads of q (fp32 [T, >= H * head_w]) in place; pairs
+    (i, i + dims / 2), or (2i, 2i + 1) when interleaved."""
     _need(("input_pos", input_pos, torch.int32), ("inv_freq", inv_freq, torch.float32), ("tail", tail, torch.float32))
     ptr, ld = _cols(_f32("q", q))
     _lib.check_seq(_lib.load_seq().cc_seq_rope_heads(ptr, ld, _p(input_pos), _p(inv_freq), q.shape[0], int(H), int(head_w), int(off),
                                                      int(seg), int(dims), _p(tail), tail.shape[-1] if tail is not None else 0,
-                                                     int(tail_off), _stream()), "cc_seq_rope_heads")
+                                                     int(tail_off), int(bool(interleaved)), _stream()), "cc_seq_rope_heads")
 
 
 def latent_expand(kv_old, kv_new, lat_old, lat_new, k_old, v_old, k_new, v_new, H, D, V, R, kv_rank):
@@ -321,12 +327,16 @@ def head_norm_gate(o, graw, nw, out, H, D, eps):
                                                          float(eps), _stream()), "cc_seq_head_norm_gate")
 
 
-def moe_route(logits, correction, ids, wts, groups, keep, top):
+def moe_route(logits, correction, ids, wts, groups, keep, top, sigmoid_scores=False, group_top=1, renormalize=True,
+              weight_scale=1.0):
+    """Router: softmax (or sigmoid) scores, choice = score + correction, the `keep` best of `groups` groups by the sum of
+    their `group_top` largest choices, `top` winners; weights = winners' scores (renormalised or not) * weight_scale."""
     _need(("correction", correction, torch.float32), ("ids", ids, torch.int32), ("wts", wts, torch.float32))
     ptr, ld = _cols(_f32("logits", logits))
     T, n = logits.shape
     _lib.check_seq(_lib.load_seq().cc_seq_moe_route(ptr, ld, _p(correction), _p(ids), _p(wts), T, n, int(groups), int(keep), int(top),
-                                                    _stream()), "cc_seq_moe_route")
+                                                    int(bool(sigmoid_scores)), int(group_top), int(bool(renormalize)),
+                                                    float(weight_scale), _stream()), "cc_seq_moe_route")
 
 
 def moe_group(ids, n_real, counts, slot, perm):
@@ -376,12 +386,13 @@ def cache_append(k_new, v_new, k_cache, v_cache, pos, mask, cache_cts, input_pos
     _lib.check_seq(_lib.load_seq().cc_seq_cache_append(C.byref(a), _stream()), "cc_seq_cache_append")
 
 
-def attention_rows(q, k_new, v_new, k_old, v_old, pos_old, input_pos, y, scale, window=0):
+def attention_rows(q, k_new, v_new, k_old, v_old, pos_old, input_pos, y, scale, window=0, sink=None):
     """Causal attention of T new tokens over n_old earlier rows and themselves, none of it through a cache object:
     q fp32 [T, H, Dk], k_new [T, G, Dk], v_new [T, G, Dv]; k_old [G, n_old, Dk], v_old [G, n_old, Dv] with pos_old
     int32 [n_old] = the position each old row holds (row j must hold position j); n_old may be 0 (pass None)."""
     _need(("q", q, torch.float32), ("k_new", k_new, None), ("v_new", v_new, k_new.dtype), ("k_old", k_old, k_new.dtype),
-          ("v_old", v_old, k_new.dtype), ("pos_old", pos_old, torch.int32), ("input_pos", input_pos, torch.int32), ("y", y, None))
+          ("v_old", v_old, k_new.dtype), ("pos_old", pos_old, torch.int32), ("input_pos", input_pos, torch.int32), ("y", y, None),
+          ("sink", sink, torch.float32))
     a = _lib.CcSeqAttn()
     T, H, Dk = q.shape
     G, Dv = k_new.shape[1], v_new.shape[-1]
@@ -393,7 +404,8 @@ def attention_rows(q, k_new, v_new, k_old, v_old, pos_old, input_pos, y, scale, 
         assert k_old.shape[0] == G and v_old.shape[:2] == k_old.shape[:2] and pos_old.numel() == k_old.shape[1]
         a.k_cache, a.v_cache, a.pos, a.L = _p(k_old), _p(v_old), _p(pos_old), k_old.shape[1]
     a.T, a.H, a.G, a.Dk, a.Dv = T, H, G, Dk, Dv
-    a.window, a.sink_mode, a.cache_dtype, a.y_dtype, a.scale = int(window), _lib.SINK_NONE, _dt(k_new), _dt(y), float(scale)
+    a.window, a.cache_dtype, a.y_dtype, a.scale = int(window), _dt(k_new), _dt(y), float(scale)
+    a.sink, a.sink_mode = _p(sink), (_lib.SINK_NONE if sink is None else _lib.SINK_LEARNED)
     _lib.check_seq(_lib.load_seq().cc_seq_attention(C.byref(a), _stream()), "cc_seq_attention")
 
 
@@ -411,13 +423,14 @@ def latent_decode_workspace_bytes(H, C, L) -> int:
     return int(_lib.load_seq().cc_seq_latent_decode_workspace(int(H), int(C), int(L)))
 
 
-def latent_decode(q, k_new, k_cache, pos, mask, cache_cts, input_pos, y, scale, workspace, append=True):
+def latent_decode(q, k_new, k_cache, pos, mask, cache_cts, input_pos, y, scale, workspace, append=True, sink=None):
     """Absorbed one-token latent attention: q fp32 [1, H, Dk] over rows k_cache [.., L, Dk] and k_new [.., Dk] (the newest
     key, appended when asked); y [1, H, C] = weighted sums of the rows' first C columns."""
     _need(("q", q, torch.float32), ("k_new", k_new, k_cache.dtype), ("k_cache", k_cache, None), ("pos", pos, torch.int32),
           ("mask", mask, torch.bool), ("cache_cts", cache_cts, torch.int32), ("input_pos", input_pos, torch.int32), ("y", y, None),
-          ("workspace", workspace, None))
+          ("workspace", workspace, None), ("sink", sink, torch.float32))
     a = _lib.CcSeqLatentDecode()
+    a.sink = _p(sink)
     a.q, a.k_new, a.k_cache, a.pos, a.mask, a.cache_cts = _p(q), _p(k_new), _p(k_cache), _p(pos), _p(mask), _p(cache_cts)
     a.input_pos, a.y = _p(input_pos), _p(y)
     a.H, a.Dk, a.C, a.L = q.shape[-2], q.shape[-1], y.shape[-1], k_cache.shape[-2]
@@ -573,3 +586,49 @@ def turn_heads_gate(y, input_pos, inv_freq, dims, interleaved, sign, gate, out):
 def softcap(x, cap):
     _need(("x", x, torch.float32))
     _lib.check_seq(_lib.load_seq().cc_seq_softcap(_p(x), x.numel(), float(cap), _stream()), "cc_seq_softcap")
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Fourth part of the C ABI (csrc/seq/par_kernels.cu): sublayers that read norms of one stream through a short
+# convolution added to its own input, whole-row query / key norms, the polynomial-of-unit-RMS activation.
+
+def par_norm(x, outs, eps, a=None, b=None, add=None, tail=None, taps=1, xhat=None):
+    """x (fp32 [T, E], in place) += a + b + add; then per entry (gain, conv_w, out) of `outs`: out = h + causal conv of h
+    over time with h = unit_rms(x) * gain (conv_w fp32 [E, taps] or None).  `tail` fp32 [taps - 1, E] carries the
+    unit-RMS rows before the step; `xhat` fp32 [T, E] is scratch for steps of several tokens."""
+    _need(("x", x, torch.float32), ("add", add, torch.float32), ("tail", tail, torch.float32), ("xhat", xhat, torch.float32))
+    g = _lib.CcSeqParNorm()
+    T, E = x.shape
+    g.x, g.add, g.xhat, g.tail = _p(x), _p(add), _p(xhat), _p(tail)
+    g.a, g.lda = _cols(_f32("a", a))
+    g.b, g.ldb = _cols(_f32("b", b))
+    assert 1 <= len(outs) <= _lib.PAR_MAX_OUT and (taps == 1 or tail.shape == (taps - 1, E))
+    for s, (gain, conv_w, out) in enumerate(outs):
+        _need(("gain", gain, torch.float32), ("conv_w", conv_w, torch.float32), ("out", out, outs[0][2].dtype))
+        assert gain.numel() == E and out.shape == (T, E) and (conv_w is None or conv_w.shape == (E, taps))
+        g.gain[s], g.conv_w[s], g.out[s] = _p(gain), _p(conv_w), _p(out)
+    g.n_out, g.act_dtype, g.T, g.E, g.taps, g.eps = len(outs), _dt(outs[0][2]), T, E, int(taps), float(eps)
+    _lib.check_seq(_lib.load_seq().cc_seq_par_norm(C.byref(g), _stream()), "cc_seq_par_norm")
+
+
+def qk_row_norm(src, off_q, nq, off_k, nk, off_v, nv, wq, wk, q_out, k_out, v_out, eps):
+    """q and k column ranges of the fused projection `src` RMS-normed over their whole width (all heads at once) with
+    gains wq / wk; v copied.  q_out fp32, k_out / v_out in the cache's type."""
+    _need(("wq", wq, torch.float32), ("wk", wk, torch.float32), ("q_out", q_out, torch.float32), ("k_out", k_out, None),
+          ("v_out", v_out, k_out.dtype))
+    a = _lib.CcSeqQkRowNorm()
+    a.inp, a.ld = _cols(_f32("src", src))
+    a.off_q, a.nq, a.off_k, a.nk, a.off_v, a.nv = int(off_q), int(nq), int(off_k), int(nk), int(off_v), int(nv)
+    T = src.shape[0]
+    assert wq.numel() == nq and wk.numel() == nk and q_out.numel() == T * nq and k_out.numel() == T * nk and v_out.numel() == T * nv
+    a.wq, a.wk, a.q_out, a.k_out, a.v_out, a.out_dtype, a.T, a.eps = _p(wq), _p(wk), _p(q_out), _p(k_out), _p(v_out), _dt(k_out), T, float(eps)
+    _lib.check_seq(_lib.load_seq().cc_seq_qk_row_norm(C.byref(a), _stream()), "cc_seq_qk_row_norm")
+
+
+def poly_norm(src, coef, out, eps):
+    """out = coef[0] N(z) + coef[1] N(z^2) + coef[2] N(z^3) + coef[3] over the rows z of `src` (fp32 column range [T, F])."""
+    _need(("coef", coef, torch.float32), ("out", out, None))
+    ptr, ld = _cols(_f32("src", src))
+    T, F = out.shape
+    assert src.shape == (T, F) and coef.numel() == 4
+    _lib.check_seq(_lib.load_seq().cc_seq_poly_norm(ptr, ld, _p(coef), _p(out), _dt(out), T, F, float(eps), _stream()), "cc_seq_poly_norm")

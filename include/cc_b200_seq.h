@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define CC_SEQ_ABI_VERSION 3
+#define CC_SEQ_ABI_VERSION 4
 
 #define CC_SEQ_OK                     0
 #define CC_SEQ_ERR_INVALID_ARG       -1
@@ -39,10 +39,13 @@ extern "C" {
 
 /*
  * One attention layer's step over a chunk of T consecutive tokens whose first position is *input_pos.
- * Query i (position p = *input_pos + i) sees key position j when j <= p and (window == 0 or p - j < window) and
- * (block == 0 or floor(p / block) == floor(j / block)): blocks are counted from position 0 of the sequence.
- * Keys j >= *input_pos are rows of k_new / v_new; older keys are read from cache slot j mod L and count only if
- * pos[slot] == j (an empty, stale or overwritten slot is not a key).
+ * Query i (position p = *input_pos + i) sees key position j when j <= p and (window == 0 or p - j < window or
+ * j < keep_first) and (block == 0 or floor(p / block) == floor(j / block)): blocks are counted from position 0 of the
+ * sequence.  Keys j >= *input_pos are rows of k_new / v_new; older keys are read from the cache slot of j and count
+ * only if pos[slot] == j (an empty, stale or overwritten slot is not a key).  Slot of j: j itself for j < keep_first,
+ * keep_first + (j - keep_first) mod (L - keep_first) otherwise (j mod L without kept positions).
+ * A scaled score s becomes softcap * tanh(s / softcap) (softcap > 0), then s - dist_a[h] * ln(1 + dist_b[h] * (p - j))
+ * (dist_a set), before the softmax.
  */
 typedef struct CcSeqAttn {
     const float* q;            /* [T, H, Dk] fp32, already normalised and scaled by the query gain */
@@ -65,6 +68,10 @@ typedef struct CcSeqAttn {
     void* workspace;           /* decode only: cc_seq_decode_workspace() bytes, zeroed once by the caller */
     uint64_t workspace_bytes;
     int32_t block;             /* 0 = none; else keys of the query's own block of `block` positions only (L >= block) */
+    int32_t keep_first;        /* with a window: the first keep_first positions stay visible and keep their slots (L >= window + keep_first) */
+    float softcap;             /* 0 = none */
+    const float* dist_a;       /* [H] fp32 or NULL: the distance penalty's factor ... */
+    const float* dist_b;       /* [H] fp32: ... and the slope inside its logarithm */
 } CcSeqAttn;
 
 int cc_seq_abi_version(void);
@@ -91,9 +98,10 @@ int cc_seq_attention(const CcSeqAttn* a, void* stream);
 /* T == 1: keys split over CTAs, partial results combined in split order by the last CTA of a head; with
  * a->append the new row is written to slot p mod L (k, v, pos, mask, cache_cts) by the same launch. */
 int cc_seq_attention_decode(const CcSeqAttn* a, void* stream);
-/* `window`: the layer's window, or its block size when it has one (the most keys a token can see; 0 = all) */
+/* `window`: the layer's window plus its kept first positions, or its block size when it has one (the most keys a token
+ * can see; 0 = all) */
 uint64_t cc_seq_decode_workspace(int32_t H, int32_t G, int32_t Dv, int32_t L, int32_t window);
-/* Writes rows of k_new / v_new into slots (p mod L); of a chunk longer than L only the last L rows. */
+/* Writes rows of k_new / v_new into their slots; of a chunk longer than the ring only the rows that stay. */
 int cc_seq_cache_append(const CcSeqAttn* a, void* stream);
 
 /* x <- unit_rms(alpha * x + y) * (1 + w), fp32 [T, E] in place; y (y_dtype) may be NULL; a copy in act dtype goes to
@@ -193,7 +201,8 @@ int cc_seq_gated_unit(const float* in, int64_t ld, int32_t off_gate, int32_t off
  *   cq[t]   = rms_norm(in[t, off_q : off_q + q_rank]) * wq                          (dtype, skipped when q_rank == 0)
  *   krow[t] = [ rms_norm(in[t, off_kv : off_kv + kv_rank]) * wkv | rot(in[t, off_kv + kv_rank : + rot_dim]) ]
  *   vrow[t] = the first kv_rank columns of krow[t] again                            (optional)
- * rot() turns pairs (i, i + rot_dims/2) of the first rot_dims entries by the angle p * inv_freq[i], p = *input_pos + t.
+ * rot() turns pairs (i, i + rot_dims/2) -- or (2i, 2i + 1) when `interleaved` -- of the first rot_dims entries by the
+ * angle p * inv_freq[i], p = *input_pos + t.
  */
 typedef struct CcSeqLatentPrep {
     const float* in;  int64_t ld;
@@ -203,15 +212,16 @@ typedef struct CcSeqLatentPrep {
     void* cq;  void* krow;  void* vrow;  int32_t dtype;
     int32_t T;
     float eps;
+    int32_t interleaved;
 } CcSeqLatentPrep;
 int cc_seq_latent_prepare(const CcSeqLatentPrep* a, void* stream);
 
 /* In place on q fp32 [T, ld] = H heads of head_w columns: the segment [off, off + seg) of every head is rotated
- * (first `dims` entries, pairs (i, i + dims/2), angle p * inv_freq[i]).  With `tail`, the segment is also copied to
- * tail[(t * H + h) * tail_ld + tail_off ...]. */
+ * (first `dims` entries, pairs (i, i + dims/2) or, when `interleaved`, (2i, 2i + 1), angle p * inv_freq[i]).  With
+ * `tail`, the segment is also copied to tail[(t * H + h) * tail_ld + tail_off ...]. */
 int cc_seq_rope_heads(float* q, int64_t ld, const int32_t* input_pos, const float* inv_freq, int32_t T, int32_t H,
                       int32_t head_w, int32_t off, int32_t seg, int32_t dims, float* tail, int64_t tail_ld,
-                      int32_t tail_off, void* stream);
+                      int32_t tail_off, int32_t interleaved, void* stream);
 
 /*
  * Per-head key / value rows from up-projected latents: kv_* fp32 [n, ld_kv] = [H*D key part | H*V values], lat_*
@@ -232,6 +242,7 @@ int cc_seq_latent_expand(const CcSeqLatentExpand* a, void* stream);
  * whose first C columns are also the value row, k_new [Dk] the row of this token (position *input_pos), which is the
  * newest key and, with `append`, is stored in slot position mod L (pos / mask / cache_cts as in CcSeqAttn).
  * y [H, C] = softmax(scale * q . row) weighted sum of the rows' first C columns.  Keys are addressed by position.
+ * With `sink` (fp32 [H]) the softmax denominator also holds exp(sink[h]): a term without key or value.
  */
 typedef struct CcSeqLatentDecode {
     const float* q;  const void* k_new;  void* k_cache;
@@ -241,6 +252,7 @@ typedef struct CcSeqLatentDecode {
     float scale;
     int32_t append;
     void* workspace;  uint64_t workspace_bytes;   /* cc_seq_latent_decode_workspace() bytes; needs no clearing */
+    const float* sink;
 } CcSeqLatentDecode;
 uint64_t cc_seq_latent_decode_workspace(int32_t H, int32_t C, int32_t L);
 int cc_seq_latent_decode(const CcSeqLatentDecode* a, void* stream);
@@ -289,12 +301,16 @@ int cc_seq_head_norm_gate(const float* o, const float* graw, int64_t ldg, const 
 
 /*
  * Router of a mixture of experts over n outputs (real and identity experts alike), logits fp32 [T, ld]:
- * scores s = softmax(logits); choice = s + correction; the outputs form `groups` equal groups of neighbours and only
- * those of the `keep` groups with the largest maximal choice can be chosen; the `top` largest choices win;
- * wts = s of the winners / (their sum + 1e-20).  ids int32 [T, top], wts fp32 [T, top].
+ * scores s = softmax(logits) over all outputs, or sigmoid(logits) each on its own (`sigmoid_scores`); choice = s +
+ * correction; the outputs form `groups` equal groups of neighbours and only those of the `keep` groups with the largest
+ * group score can be chosen (the others count as minus infinity), a group's score being the sum of its `group_top`
+ * largest choices (1 = its maximum); the `top` largest choices win (the lower index on a tie);
+ * wts = s of the winners / (their sum + 1e-20) when `renormalize`, else s; both times weight_scale.
+ * ids int32 [T, top], wts fp32 [T, top].
  */
 int cc_seq_moe_route(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* wts, int32_t T,
-                     int32_t n, int32_t groups, int32_t keep, int32_t top, void* stream);
+                     int32_t n, int32_t groups, int32_t keep, int32_t top, int32_t sigmoid_scores, int32_t group_top,
+                     int32_t renormalize, float weight_scale, void* stream);
 
 /* Groups the M = T * top (token, choice) pairs by real expert (id < n_real): counts [n_real], slot [M] = row of the
  * pair in expert order (-1 for an identity expert), perm [M] = token of each row. */
@@ -309,7 +325,8 @@ int cc_seq_moe_expert_tokens(const void* Wgu, const void* Wd, const void* h, con
                              void* stream);
 
 /* out[t] = sum_k wts[t, k] * (ids[t, k] < n_real ? y[slot[t, k]] : h[t]) + sigmoid(sg[t * ld_sg]) * shared[t];
- * slot == NULL means row t * top + k; shared may be NULL; sg == NULL means no gate on it. */
+ * slot == NULL means row t * top + k; shared may be NULL; sg == NULL means no gate on it; h may be NULL when there are
+ * no identity experts. */
 typedef struct CcSeqMoeCombine {
     const int32_t* ids;  const float* wts;  const int32_t* slot;
     const float* y;  const float* h;  const float* shared;  const float* sg;  int64_t ld_sg;
@@ -441,6 +458,56 @@ int cc_seq_turn_heads_gate(const float* y, const int32_t* input_pos, const float
 
 /* x <- cap * tanh(x / cap), fp32, n elements, in place */
 int cc_seq_softcap(float* x, int64_t n, float cap, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Fourth part (csrc/seq/par_kernels.cu): layers whose sublayers read norms of the same stream, each through a short
+ * causal convolution added to its own input; whole-row query / key norms; the polynomial-of-unit-RMS activation.
+ * ------------------------------------------------------------------------------------------------------------------ */
+
+/*
+ * Residual sum + one unit-RMS pass + up to CC_PAR_MAX_OUT sublayer inputs.  Per row t of the fp32 stream x [T, E]:
+ *   x[t] += a[t] + b[t] + add              (each optional: the sublayer results of the layer before, a vector per pass)
+ *   xh[t] = x[t] / sqrt(mean(x[t]^2) + eps)
+ *   h_s[t] = xh[t] * gain_s;   out_s[t] = h_s[t] + sum_j conv_w_s[c, j] * h_s[t - taps + 1 + j]    (conv_w_s NULL: h_s[t])
+ * The rows before the step's first token come from `tail` fp32 [taps - 1, E] (unit-RMS rows xh, oldest first; zeros
+ * at a sequence's start), which afterwards holds the step's last taps - 1 rows.  conv_w_s fp32 [E, taps], the last
+ * tap meets the current token.  out_s [T, E] in act_dtype.  xhat fp32 [T, E] is scratch (needed when T > 1).
+ */
+#define CC_PAR_MAX_OUT 4
+typedef struct CcSeqParNorm {
+    float* x;
+    const float* a;  int64_t lda;
+    const float* b;  int64_t ldb;
+    const float* add;
+    float* xhat;
+    float* tail;
+    const float* gain[CC_PAR_MAX_OUT];
+    const float* conv_w[CC_PAR_MAX_OUT];
+    void* out[CC_PAR_MAX_OUT];
+    int32_t n_out, act_dtype, T, E, taps;
+    float eps;
+} CcSeqParNorm;
+int cc_seq_par_norm(const CcSeqParNorm* g, void* stream);
+
+/*
+ * From fp32 rows `in` [T, ld]: q (nq columns at off_q) and k (nk columns at off_k) are each divided by the root mean
+ * square of the whole range (all heads at once) and multiplied by wq [nq] / wk [nk]; v (nv columns at off_v) is copied.
+ * q_out fp32 [T, nq]; k_out [T, nk] and v_out [T, nv] in out_dtype.
+ */
+typedef struct CcSeqQkRowNorm {
+    const float* in;  int64_t ld;
+    int32_t off_q, nq, off_k, nk, off_v, nv;
+    const float* wq;  const float* wk;
+    float* q_out;  void* k_out;  void* v_out;
+    int32_t out_dtype, T;
+    float eps;
+} CcSeqQkRowNorm;
+int cc_seq_qk_row_norm(const CcSeqQkRowNorm* a, void* stream);
+
+/* out[t] = coef[0] N(z) + coef[1] N(z^2) + coef[2] N(z^3) + coef[3], z = in[t, 0:F] (fp32 [T, ld]), powers element by
+ * element, N(u) = u / sqrt(mean(u^2) + eps) over the F columns; coef fp32 [4] on the device; out [T, F] in out_dtype. */
+int cc_seq_poly_norm(const float* in, int64_t ld, const float* coef, void* out, int32_t out_dtype, int32_t T, int32_t F,
+                     float eps, void* stream);
 
 #ifdef __cplusplus
 }
