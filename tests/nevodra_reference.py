@@ -75,14 +75,16 @@ def window_attention(h, W, p, m, eps):
     q = rms_norm(h @ W[p + "q"].T, W[p + "q.norm"], eps).view(T, H, D)
     k = rms_norm(h @ W[p + "k"].T, W[p + "k.norm"], eps).view(T, G, D)
     v = (h @ W[p + "v"].T).view(T, G, V)
-    ok = window_mask(T, m["mask"]["size"], m["mask"]["keep_first"])
+    mask = m.get("mask")                      # no mask in the configuration: every earlier key
+    ok = window_mask(T, mask["size"], mask.get("keep_first", 0)) if mask else window_mask(T, T, 0)
     dist = (torch.arange(T)[:, None] - torch.arange(T)[None, :]).clamp(min=0).to(h.dtype)
-    cap = float(m["softcap"])
+    cap = float(m.get("softcap") or 0.0)      # no cap when the configuration gives none
     out = h.new_zeros(T, H, V)
     for hh in range(H):
         g = hh // (H // G)
         s = (q[:, hh] @ k[:, g].T) * float(m["scale"])
-        s = cap * torch.tanh(s / cap)
+        if cap:
+            s = cap * torch.tanh(s / cap)
         s = s - W[p + "r1"][hh] * torch.log(1 + W[p + "r2"][hh] * dist)
         s = s.masked_fill(~ok, float("-inf"))
         out[:, hh] = torch.softmax(s, -1) @ v[:, g]

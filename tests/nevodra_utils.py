@@ -22,9 +22,12 @@ def moe(experts=6, top=2, ff=24, count=3, keep=2, scale=1.3, shared=40):
 
 
 def window_layer(mlp=None, heads=4, kv_heads=2, dim=16, vdim=12, size=13, keep_first=3, scale=None, softcap=8.0):
-    return {"type": "attention", "mlp": mlp,
-            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale or dim ** -0.5,
-                      "softcap": softcap, "mask": {"size": size, "keep_first": keep_first}}}
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale or dim ** -0.5}
+    if size:
+        mixer["mask"] = {"size": size, "keep_first": keep_first}
+    if softcap:
+        mixer["softcap"] = softcap
+    return {"type": "attention", "mlp": mlp, "mixer": mixer}
 
 
 def latent_layer(mlp=None, heads=3, dim=12, rot_dim=8, vdim=20, kv_rank=24, base=300.0, dims=None, scale=None):
@@ -50,8 +53,12 @@ def default_layers():
 DEFAULT_LOOP = (1, 3, 3)     # layers 1 and 2 run three times in a row
 
 
-def random_weights(cfg, seed=0):
-    """bf16 tensors under the checkpoint's names; gains and coefficients away from their neutral values."""
+def random_weights(cfg, seed=0, decisive=False):
+    """bf16 tensors under the checkpoint's names; gains and coefficients away from their neutral values.  `decisive`
+    spaces the routers' corrections further apart than the scores can vary, so that no choice is a close call: with
+    random corrections a few tokens sit where two choice scores differ by less than the bf16 error of the router's
+    input, either choice is a correct bf16 result, and the tokens after such a one see it too.  The bf16 runs of the
+    model use decisive weights and are held to a bar for every position; the fp32 runs route by the scores."""
     g = torch.Generator().manual_seed(seed)
     E, V = cfg["width"], cfg["vocab"]
     taps = cfg["canon"]["taps"]
@@ -92,7 +99,7 @@ def random_weights(cfg, seed=0):
         else:
             n, F = mlp["router"]["experts"], mlp["expert"]["ff"]
             W[q + "router"] = rnd(n, E, s=E ** -0.5 * 2.0)
-            W[q + "correction"] = rnd(n, s=0.3)
+            W[q + "correction"] = (torch.randperm(n, generator=g) * 1.5 - 2.0).to(torch.bfloat16) if decisive else rnd(n, s=0.3)
             names = [f"e{e}." for e in range(n)] + (["shared."] if mlp.get("shared") else [])
             for name in names:
                 Fe = mlp["shared"]["ff"] if name == "shared." else F
@@ -137,11 +144,10 @@ def run_portions(model, tokens, portions, device="cuda"):
 
 
 def assert_rows_close(err, dtype, tol, what=""):
-    """err: one error per position.  fp32: every position within `tol`.  bf16: the median within a third of `tol` and at
-    most one position in twenty beyond it (with random weights a few tokens sit where two experts' choice scores differ
-    by less than a bf16 rounding of the router's input; either choice is a correct bf16 result)."""
+    """err: one error per position.  fp32: every position within `tol`.  bf16: the median within a third of `tol` and no
+    position beyond it."""
     err = torch.as_tensor(err).double().reshape(-1)
     if dtype == torch.bfloat16:
-        assert (err > tol).double().mean() <= 0.05 and err.median() < tol / 3, (what, err.median().item(), err.max().item())
+        assert err.max() < tol and err.median() < tol / 3, (what, err.median().item(), err.max().item())
     else:
         assert err.max() < tol, (what, err.max().item(), int(err.argmax()))

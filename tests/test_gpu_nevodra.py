@@ -313,7 +313,7 @@ def test_sink_takes_its_share_and_a_far_key_is_found(mode):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_layers_one_by_one_and_logits(dtype):
     cfg = make_config(default_layers(), loop=DEFAULT_LOOP)
-    W = random_weights(cfg, seed=5)
+    W = random_weights(cfg, seed=5, decisive=dtype == torch.bfloat16)
     tokens = torch.randint(0, cfg["vocab"], (41,), generator=torch.Generator().manual_seed(6)).tolist()
     ref_layers = []
     want = reference_logits(cfg, W, tokens, ref_layers)
@@ -333,7 +333,7 @@ def test_layers_one_by_one_and_logits(dtype):
                          ids=["token_by_token", "whole", "twos", "mixed", "around_window_edges", "last_alone"])
 def test_prompt_portions_and_decoding_agree_with_the_whole(dtype, portions):
     cfg = make_config(default_layers(), loop=DEFAULT_LOOP)
-    W = random_weights(cfg, seed=9)
+    W = random_weights(cfg, seed=9, decisive=dtype == torch.bfloat16)
     tokens = torch.randint(0, cfg["vocab"], (70,), generator=torch.Generator().manual_seed(10)).tolist()
     want = reference_logits(cfg, W, tokens)
     model = build_model(cfg, W, dtype, 70)
@@ -345,7 +345,7 @@ def test_prompt_portions_and_decoding_agree_with_the_whole(dtype, portions):
 def test_one_token_kernels_equal_the_portion_kernels(dtype):
     """A decode step through the one-token product kernels against the same step through library products."""
     cfg = make_config(default_layers(), loop=DEFAULT_LOOP)
-    W = random_weights(cfg, seed=15)
+    W = random_weights(cfg, seed=15, decisive=dtype == torch.bfloat16)
     tokens = torch.randint(0, cfg["vocab"], (50,), generator=torch.Generator().manual_seed(16)).tolist()
     outs = []
     for fused in (True, False):
@@ -412,7 +412,7 @@ OTHER = [
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_other_sizes(layers, kw, dtype):
     cfg = make_config(layers, **kw)
-    W = random_weights(cfg, seed=21)
+    W = random_weights(cfg, seed=21, decisive=dtype == torch.bfloat16)
     tokens = torch.randint(0, cfg["vocab"], (48,), generator=torch.Generator().manual_seed(22)).tolist()
     want = reference_logits(cfg, W, tokens)
     model = build_model(cfg, W, dtype, 48)
@@ -466,7 +466,7 @@ def test_trace_replay_command(tmp_path):
     root = Path(__file__).resolve().parent.parent
     cfg = make_config([latent_layer(dense(40)), window_layer(moe(), size=32, keep_first=5), window_layer(None), latent_layer(moe(shared=0))],
                       width=72, vocab=211, loop=(1, 3, 2))
-    W = random_weights(cfg, seed=31)
+    W = random_weights(cfg, seed=31, decisive=True)
     model_dir = tmp_path / "ckpt"
     model_dir.mkdir()
     (model_dir / "config.json").write_text(json.dumps(cfg))
