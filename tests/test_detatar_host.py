@@ -177,4 +177,4 @@ def test_new_entry_points_validate_their_arguments():
         setattr(w, name, fake)
     w.T, w.H, w.D = 1, 1, 300
     assert lib.cc_seq_wkv(C.byref(w), None) < 0 and "256" in err()
-    assert lib.cc_seq_moe_route(fake, 8, None, fake, fake, 3, 8, 3, 1, 2, None) < 0 and "moe_route" in err()   # 3 groups of 8 outputs
+    assert lib.cc_seq_moe_route(fake, 8, None, fake, fake, 3, 8, 3, 1, 2, 0, 1, 1, 1.0, None) < 0 and "moe_route" in err()   # 3 groups of 8 outputs

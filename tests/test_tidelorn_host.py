@@ -92,10 +92,10 @@ def test_cache_plan_follows_the_layer_types():
         model(torch.zeros(1, 3, dtype=torch.int32), torch.arange(3), True)
 
 
-def test_window_cache_with_global_tokens_refuses_position_addressing():
+def test_window_cache_with_global_tokens_keeps_them_and_scored_policies_refuse_position_addressing():
     from cold_compress_b200.cache import KVCacheHeavyHitter, KVCacheRecentGlobal
     c = KVCacheRecentGlobal(1, 2, 8, torch.float32, max_cache_length=16, global_tokens=4, max_seq_length=64, cache_bits=None)
-    assert c.sequence_window() is None
+    assert c.sequence_window() == 12 and c.sequence_kept() == 4      # the first four positions keep their slots, a ring of 12
     h = KVCacheHeavyHitter(1, 2, 8, torch.bfloat16, max_cache_length=16, global_tokens=1, max_seq_length=64, cache_bits=None,
                            history_window_size=1, recent_window=4, attn_thresholding=False)
     assert h.sequence_window() is None and h.v_head_dim == 8
