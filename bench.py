@@ -776,6 +776,55 @@ def _tefovik_model(sz, device, dtype):
     return model.eval()
 
 
+NEVODRA_KEEP_FIRST = 64      # first positions a windowed layer keeps beside its window
+
+
+def _nevodra_config(sz, extra):
+    """Latent-attention layers (the shape's head count, 96 + 32 key columns, 128 value columns, the same key/value rank
+    as the Detatar arm, full-rank queries) alternate with windowed layers (the shape's heads and window, 64 kept first
+    positions); feed-forwards alternate between the shape's dense size and experts (16, 4 chosen, 4 groups of which 2,
+    a shared one) as in the Detatar arm.  No loop: as many layer runs as the other arm has layers."""
+    E, D = sz["width"], sz["head"]
+    latent = {"heads": sz["heads"], "dim": 96, "rot_dim": 32, "vdim": D, "kv_rank": extra["kv_rank"], "scale": 128 ** -0.5,
+              "rot": {"base": 1000000.0, "dims": 32}}
+    window = {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 30.0,
+              "mask": {"size": sz["window"], "keep_first": NEVODRA_KEEP_FIRST}}
+    dense = {"kind": "dense", "ff": sz["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": extra["expert_ff"]}, "shared": {"ff": extra["shared_ff"]},
+           "router": {"experts": 16, "top": 4, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+    layers = [{"type": "latent_attention" if i % 2 == 0 else "attention", "mixer": latent if i % 2 == 0 else window,
+               "mlp": dense if i % 4 in (0, 3) else moe} for i in range(sz["layers"])]
+    return {"architecture": "Nevodra", "vocab": sz["vocab"], "width": E, "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+            "embedding": {"scale": E ** 0.5}, "layers": layers}
+
+
+def _nevodra_model(sz, extra, device, dtype):
+    from cold_compress_b200.nevodra import NevodraTransformer
+    with torch.device(device):
+        model = NevodraTransformer.from_config(_nevodra_config(sz, extra), dtype)
+    gen = torch.Generator(device=device).manual_seed(0)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if name.endswith("norms.conv"):
+                p.fill_(1.0 / p.shape[-1])
+            elif p.dim() >= 2 and not name.endswith("norms.weight"):
+                p.copy_(torch.empty(p.shape, device=device).normal_(0.0, 0.02, generator=gen))
+            elif name.endswith(("dist_a", "dist_b")):
+                p.fill_(0.5)
+            elif name.endswith(("sink", "correction")):
+                p.zero_()
+            elif name.endswith("coef"):
+                p.copy_(torch.tensor([1.0, 0.3, 0.1, 0.0], device=device))
+            else:
+                p.fill_(1.0)
+        for layer in model.layers:
+            if layer.block.kind == "latent_attention":
+                m = layer.block.mixer
+                H, D, C = m.heads, m.head_dim, m.kv_rank
+                m.w_uk_t.copy_(m.w_ukv[:H * D].reshape(H, D, C).transpose(1, 2))
+    return model.eval()
+
+
 def _llama_model(sz, device):
     from cold_compress_b200.model import ModelArgs, Transformer
     cfg = ModelArgs(block_size=sz["prompt"] + 1024, vocab_size=sz["vocab"], n_layer=sz["layers"], n_head=sz["heads"],
@@ -819,7 +868,8 @@ def run_design(args):
     names = [n for n in args.design.split(",") if n]
     flush = torch.zeros(64 << 20, dtype=torch.float32, device=device)
     rows = []
-    arms = {"detatar": ("detatar", "tidelorn"), "tefovik": ("tefovik", "detatar")}.get(args.design_model, ("tidelorn", "llama"))
+    arms = {"detatar": ("detatar", "tidelorn"), "tefovik": ("tefovik", "detatar"),
+            "nevodra": ("nevodra", "detatar")}.get(args.design_model, ("tidelorn", "llama"))
     for name in names:
         sz = DESIGN_SIZES[name]
         P = sz["prompt"]
@@ -827,6 +877,7 @@ def run_design(args):
         row = {"size": name, **sz}
         for arm in arms:
             model = (_detatar_model(sz, DETATAR_SIZES[name], device, torch.bfloat16) if arm == "detatar" else
+                     _nevodra_model(sz, DETATAR_SIZES[name], device, torch.bfloat16) if arm == "nevodra" else
                      _tefovik_model(sz, device, torch.bfloat16) if arm == "tefovik" else
                      _tidelorn_model(sz, device, torch.bfloat16) if arm == "tidelorn" else _llama_model(sz, device))
             ck = cache_kwargs(dict(slots=1.0, pattern="tile", strategy="full", compressor="recent_global"))
@@ -861,7 +912,7 @@ def run_design(args):
                 torch.cuda.synchronize()
                 dms = a.elapsed_time(b) / args.steps
             wbytes = sum(p.numel() * p.element_size() for n, p in model.named_parameters() if p.dim() >= 2 and "tok_embeddings" not in n and "bigram" not in n)
-            if arm == "detatar":      # a token reads `top` experts of each mixture, not all of them, and one copy of W_uk
+            if arm in ("detatar", "nevodra"):      # a token reads `top` experts of each mixture, not all of them, and one copy of W_uk
                 for layer in model.layers:
                     f, m = layer.block.mlp, layer.block.mixer
                     if hasattr(f, "w_gu"):
@@ -875,12 +926,15 @@ def run_design(args):
             del model, decoder
             torch.cuda.empty_cache()
         row["kernels"] = _design_kernels(sz, device, hbm)
-        if args.design_model in ("detatar", "tefovik"):
+        if args.design_model in ("detatar", "tefovik", "nevodra"):
             row["detatar_kernels"] = _detatar_kernels(sz, DETATAR_SIZES[name], device, hbm)
+        if args.design_model == "nevodra":
+            row["nevodra_kernels"] = _nevodra_kernels(sz, DETATAR_SIZES[name], device, hbm)
         if args.design_model == "tefovik":
             row["tefovik_kernels"] = _tefovik_kernels(sz, device, hbm)
         rows.append(row)
-    metric = ("prefill and decode tokens/s, Detatar beside Tidelorn at equal layer shape" if args.design_model == "detatar" else
+    metric = ("prefill and decode tokens/s, Nevodra beside Detatar at equal layer shape" if args.design_model == "nevodra" else
+              "prefill and decode tokens/s, Detatar beside Tidelorn at equal layer shape" if args.design_model == "detatar" else
               "prefill and decode tokens/s, Tefovik beside Detatar at equal layer shape" if args.design_model == "tefovik" else
               "prefill and decode tokens/s, Tidelorn beside Llama (full cache) at equal layer shape")
     print(json.dumps({"metric": metric,
@@ -1065,6 +1119,93 @@ def _tefovik_kernels(sz, device, hbm):
     return out
 
 
+def _nevodra_kernels(sz, extra, device, hbm):
+    """The Nevodra kernels alone at this shape: windowed attention with kept first positions, soft cap and distance
+    penalty over a prompt and for one token (beside `prefill_attention_window` / `decode_attention_window`, the same
+    kernels with a plain window), the absorbed one-token latent attention with a sink, the sum + two norms + input
+    convolutions of a layer over a prompt and for one token, and both activations' passes."""
+    from cold_compress_b200 import seq_ops
+    from cold_compress_b200.cache import get_cache_constructor
+    P, E, F = sz["prompt"], sz["width"], sz["ff"]
+    H, G, D, W, K = sz["heads"], sz["kv_heads"], sz["head"], sz["window"], NEVODRA_KEEP_FIRST
+    gen = torch.Generator(device=device).manual_seed(5)
+    out = {}
+
+    def token_us(fn):
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(20):
+                fn()
+        return _time_events(graph.replay, 2, 5) * 1e3 / 20
+
+    q = torch.randn(P, H, D, device=device, generator=gen)
+    k, v = (torch.randn(P, G, D, device=device, generator=gen).to(torch.bfloat16) for _ in range(2))
+    y = torch.empty(P, H, D, device=device, dtype=torch.bfloat16)
+    da, db = torch.full((H,), 0.5, device=device), torch.full((H,), 0.5, device=device)
+    ctor, _ = get_cache_constructor("recent_global")
+    with torch.device(device):
+        cache = ctor(1, G, D, torch.bfloat16, max_cache_length=W + K, global_tokens=K, max_seq_length=P + 8, cache_bits=None)
+    ip0 = torch.zeros(1, dtype=torch.int32, device=device)
+    args = (q, k, v, cache.k_cache, cache.v_cache, cache.pos, cache.mask, cache.cache_cts, ip0, y, None, W, 0, D ** -0.5)
+    shaped = (0, K, 30.0, da, db)
+    ms = _time_events(lambda: seq_ops.seq_attention(*args, seq_ops.ATTN_CHUNK, None, *shaped), 2, 3)
+    pairs = sum(min(i + 1, W) + min(K, max(0, i + 1 - W)) for i in range(P))
+    out["prefill_attention_window_kept"] = {"ms": round(ms, 3), "fp32_tflops": round(4 * pairs * D * H / ms / 1e9, 2)}
+    seq_ops.seq_attention(*args, seq_ops.ATTN_APPEND_ONLY, None, *shaped)
+    ipd = torch.tensor([P], dtype=torch.int32, device=device)
+    ws = cache._sequence_workspace(H, W + K)
+    dargs = (q[:1], k[:1], v[:1], cache.k_cache, cache.v_cache, cache.pos, cache.mask, cache.cache_cts, ipd, y[:1], None, W, 0, D ** -0.5)
+    us = token_us(lambda: seq_ops.seq_attention(*dargs, seq_ops.ATTN_DECODE, ws, *shaped))
+    nbytes = 2 * G * (W + K) * D * 2
+    out["decode_attention_window_kept"] = {"us": round(us, 2), "gb_per_s": round(nbytes / us / 1e3, 1), "frac_of_hbm": round(nbytes / us / 1e3 / hbm, 3)}
+    # absorbed latent attention with a sink
+    C, R = extra["kv_rank"], 32
+    ctor, _ = get_cache_constructor("latent")
+    with torch.device(device):
+        lat = ctor(1, 1, C + R, torch.bfloat16, v_head_dim=C, max_cache_length=P + 8, max_seq_length=P + 8)
+    rows = torch.randn(P, 1, C + R, device=device, generator=gen).to(torch.bfloat16)
+    lat.sequence_append(rows, ip0)
+    ql = torch.randn(1, H, C + R, device=device, generator=gen)
+    yl = torch.empty(1, H, C, device=device, dtype=torch.bfloat16)
+    sink = torch.zeros(H, device=device)
+    us = token_us(lambda: lat.latent_step(ql, rows[:1], ipd, yl, 0.1, sink=sink))
+    nbytes = P * (C + R) * 2
+    out["decode_attention_latent_sink"] = {"us": round(us, 2), "launches": 2, "gb_per_s": round(nbytes / us / 1e3, 1),
+                                           "frac_of_hbm": round(nbytes / us / 1e3 / hbm, 3)}
+    # sum + two norms + input convolutions
+    taps = 4
+    x = torch.randn(P, E, device=device, generator=gen)
+    a, b = torch.randn(P, E, device=device, generator=gen), torch.randn(P, E, device=device, generator=gen)
+    gains = [torch.ones(E, device=device) for _ in range(2)]
+    convs = [torch.full((E, taps), 0.25, device=device) for _ in range(2)]
+    outs = [torch.empty(P, E, device=device, dtype=torch.bfloat16) for _ in range(2)]
+    tail, rinv = torch.zeros(taps - 1, E, device=device), torch.empty(P, device=device)
+    spec = [(gains[i], convs[i], outs[i]) for i in range(2)]
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=device)
+    ms = _time_events(lambda: seq_ops.par_norm(x, spec, 1e-5, a=a, b=b, tail=tail, taps=taps, rinv=rinv), 2, 3, flush)
+    nbytes = P * E * (4 * 4 + 4 + 2 * 2)           # x read and written, a, b read; x read again; two bf16 outputs
+    out["sum_norms_canon_prompt"] = {"ms": round(ms, 3), "launches": 3, "gb_per_s": round(nbytes / ms / 1e6, 1), "frac_of_hbm": round(nbytes / ms / 1e6 / hbm, 3)}
+    spec1 = [(gains[i], convs[i], outs[i][:1]) for i in range(2)]
+    x1 = torch.empty(1, E, device=device)
+    us = token_us(lambda: seq_ops.par_norm(x[:1], spec1, 1e-5, a=a[:1], b=b[:1], tail=tail, taps=taps, x_out=x1))
+    out["sum_norms_canon_token"] = {"us": round(us, 2), "launches": 1}
+    # activations: polynomial of unit RMS over the dense size, beside the gated unit the other arm's dense layer uses
+    up = torch.randn(P, 2 * F, device=device, generator=gen)
+    coef = torch.tensor([1.0, 0.3, 0.1, 0.0], device=device)
+    act = torch.empty(P, F, device=device, dtype=torch.bfloat16)
+    ms = _time_events(lambda: seq_ops.poly_norm(up[:, :F], coef, act, 1e-5), 2, 3, flush)
+    nbytes = P * F * (2 * 4 + 2)                    # the row is read twice (statistics, then values) and written once
+    out["poly_norm_prompt"] = {"ms": round(ms, 3), "gb_per_s": round(nbytes / ms / 1e6, 1), "frac_of_hbm": round(nbytes / ms / 1e6 / hbm, 3)}
+    ms = _time_events(lambda: seq_ops.gated_unit(up, 0, F, act, 1), 2, 3, flush)
+    nbytes = P * F * (2 * 4 + 2)
+    out["gated_unit_prompt"] = {"ms": round(ms, 3), "gb_per_s": round(nbytes / ms / 1e6, 1), "frac_of_hbm": round(nbytes / ms / 1e6 / hbm, 3)}
+    us = token_us(lambda: seq_ops.poly_norm(up[:1, :F], coef, act[:1], 1e-5))
+    out["poly_norm_token"] = {"us": round(us, 2)}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1077,9 +1218,9 @@ def main():
     ap.add_argument("--design", default="", metavar="SIZES",
                     help="instead of the headline workload: Tidelorn beside the Llama-family model at equal layer shape, "
                          "comma-separated sizes of " + "/".join(DESIGN_SIZES))
-    ap.add_argument("--design-model", default="tidelorn", choices=["tidelorn", "detatar", "tefovik"],
+    ap.add_argument("--design-model", default="tidelorn", choices=["tidelorn", "detatar", "tefovik", "nevodra"],
                     help="with --design: which design is measured (tidelorn: beside the Llama-family model; detatar: beside "
-                         "Tidelorn; tefovik: beside Detatar; sizes " + "/".join(DETATAR_SIZES) + ")")
+                         "Tidelorn; tefovik, nevodra: beside Detatar; sizes " + "/".join(DETATAR_SIZES) + ")")
     args = ap.parse_args()
     if args.design:
         return run_design(args)

@@ -288,7 +288,7 @@ PAR_MAX_OUT = 4
 
 
 class CcSeqParNorm(C.Structure):
-    _fields_ = [("x", _vp), ("a", _vp), ("lda", _i64), ("b", _vp), ("ldb", _i64), ("add", _vp), ("xhat", _vp), ("tail", _vp),
+    _fields_ = [("x", _vp), ("a", _vp), ("lda", _i64), ("b", _vp), ("ldb", _i64), ("add", _vp), ("rinv", _vp), ("x_out", _vp), ("tail", _vp),
                 ("gain", _vp * PAR_MAX_OUT), ("conv_w", _vp * PAR_MAX_OUT), ("out", _vp * PAR_MAX_OUT)] + [
         (n, _i32) for n in ("n_out", "act_dtype", "T", "E", "taps")] + [("eps", _f32)]
 

@@ -102,11 +102,15 @@ class ParallelNorms(nn.Module):
         self.weight = _zeros(self.n, dim, dtype=torch.float32)
         self.conv = _zeros(self.n, dim, self.taps, dtype=torch.float32)
 
-    def forward(self, x: Tensor, outs: List[Tensor], tail: Tensor, pending: Optional[dict] = None, add: Optional[Tensor] = None):
+    def forward(self, x: Tensor, outs: List[Tensor], tail: Tensor, pending: Optional[dict] = None, add: Optional[Tensor] = None) -> Tensor:
+        """Returns the stream after the sum: x itself (updated in place) for steps of several tokens, a new row for one
+        token (the launch spreads the row over the GPU, and the CTAs that still read the old row must not see it change)."""
         T = x.shape[0]
-        xhat = torch.empty_like(x) if T > 1 else None
+        rinv = torch.empty(T, dtype=torch.float32, device=x.device) if T > 1 else None
+        x_out = torch.empty_like(x) if T == 1 else None
         seq_ops.par_norm(x, [(self.weight[s], self.conv[s], outs[s]) for s in range(self.n)], self.eps, add=add,
-                         tail=tail if self.taps > 1 else None, taps=self.taps, xhat=xhat, **(pending or {}))
+                         tail=tail if self.taps > 1 else None, taps=self.taps, rinv=rinv, x_out=x_out, **(pending or {}))
+        return x if x_out is None else x_out
 
 
 class WindowAttention(nn.Module):
@@ -221,23 +225,22 @@ class NevodraBlock(nn.Module):
         T, E = x.shape
         dt = self.mixer.w_in.dtype
         hs = [torch.empty(T, E, dtype=dt, device=x.device) for _ in range(self.norms.n)]
-        self.norms(x, hs, state.vectors, pending, add)
-        return hs
+        return hs, self.norms(x, hs, state.vectors, pending, add)
 
     def forward(self, x: Tensor, ip: Tensor, state, kv_cache, pending: Optional[dict], add: Optional[Tensor],
-                one_token_kernel: bool) -> dict:
+                one_token_kernel: bool):
         """Applies the pending sum of the layer before (and the pass's vector), runs this layer's sublayers on the two
-        norms of the result and returns them as the next pending sum."""
-        hs = self._inputs(x, state, pending, add)
+        norms of the result and returns (the stream after the sum, the sublayer results as the next pending sum)."""
+        hs, x = self._inputs(x, state, pending, add)
         out = dict(a=self.mixer(hs[0], ip, kv_cache, one_token_kernel))
         if self.mlp is not None:
             out["b"] = self.mlp(_proj(hs[1], self.w_ff), 0, None, hs[1], one_token_kernel)
-        return out
+        return x, out
 
-    def step_one_token(self, x: Tensor, ip: Tensor, state, kv_cache, pending: Optional[dict], add: Optional[Tensor]) -> dict:
+    def step_one_token(self, x: Tensor, ip: Tensor, state, kv_cache, pending: Optional[dict], add: Optional[Tensor]):
         """The same layer for one token: sum + norms + convolutions in one launch; every product that reads a sublayer
         input in one launch; the mixer's core; the products that close the sublayers in one launch."""
-        hs = self._inputs(x, state, pending, add)
+        hs, x = self._inputs(x, state, pending, add)
         jobs, outs = self.mixer.first_jobs(hs[0])
         hp = None
         if self.mlp is not None:
@@ -254,7 +257,7 @@ class NevodraBlock(nn.Module):
         out = dict(a=mixed)
         if result is not None:
             out["b"] = result()
-        return out
+        return x, out
 
     def one_token_fits(self) -> bool:
         return self.kind == "attention" or self.mixer.absorbed_fits()
@@ -399,9 +402,9 @@ class NevodraTransformer(nn.Module):
         for layer in self.layers:
             add = self.loop_step[layer.step_row] if layer.step_row is not None else None
             if one and layer.block.one_token_fits():
-                pending = layer.block.step_one_token(x, ip, layer.state, layer.kv_cache, pending, add)
+                x, pending = layer.block.step_one_token(x, ip, layer.state, layer.kv_cache, pending, add)
             else:
-                pending = layer.block(x, ip, layer.state, layer.kv_cache, pending, add, self.fused_decode)
+                x, pending = layer.block(x, ip, layer.state, layer.kv_cache, pending, add, self.fused_decode)
             if collect is not None:
                 seq_ops.gated_group_norm(x, None, 1, 0.0, **pending)
                 pending = None

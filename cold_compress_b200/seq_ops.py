@@ -592,14 +592,17 @@ def softcap(x, cap):
 # Fourth part of the C ABI (csrc/seq/par_kernels.cu): sublayers that read norms of one stream through a short
 # convolution added to its own input, whole-row query / key norms, the polynomial-of-unit-RMS activation.
 
-def par_norm(x, outs, eps, a=None, b=None, add=None, tail=None, taps=1, xhat=None):
+def par_norm(x, outs, eps, a=None, b=None, add=None, tail=None, taps=1, rinv=None, x_out=None):
     """x (fp32 [T, E], in place) += a + b + add; then per entry (gain, conv_w, out) of `outs`: out = h + causal conv of h
     over time with h = unit_rms(x) * gain (conv_w fp32 [E, taps] or None).  `tail` fp32 [taps - 1, E] carries the
-    unit-RMS rows before the step; `xhat` fp32 [T, E] is scratch for steps of several tokens."""
-    _need(("x", x, torch.float32), ("add", add, torch.float32), ("tail", tail, torch.float32), ("xhat", xhat, torch.float32))
+    unit-RMS rows before the step; `rinv` fp32 [T] is scratch for steps of several tokens.  `x_out` (one token): the
+    summed row goes there instead of into x, and the launch spreads the row's channels over the GPU."""
+    _need(("x", x, torch.float32), ("x_out", x_out, torch.float32), ("add", add, torch.float32), ("tail", tail, torch.float32), ("rinv", rinv, torch.float32))
     g = _lib.CcSeqParNorm()
     T, E = x.shape
-    g.x, g.add, g.xhat, g.tail = _p(x), _p(add), _p(xhat), _p(tail)
+    assert rinv is None or rinv.numel() >= T
+    assert x_out is None or (x_out.shape == x.shape and x_out.data_ptr() != x.data_ptr())
+    g.x, g.add, g.rinv, g.tail, g.x_out = _p(x), _p(add), _p(rinv), _p(tail), _p(x_out)
     g.a, g.lda = _cols(_f32("a", a))
     g.b, g.ldb = _cols(_f32("b", b))
     assert 1 <= len(outs) <= _lib.PAR_MAX_OUT and (taps == 1 or tail.shape == (taps - 1, E))

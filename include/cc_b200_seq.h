@@ -471,7 +471,8 @@ int cc_seq_softcap(float* x, int64_t n, float cap, void* stream);
  *   h_s[t] = xh[t] * gain_s;   out_s[t] = h_s[t] + sum_j conv_w_s[c, j] * h_s[t - taps + 1 + j]    (conv_w_s NULL: h_s[t])
  * The rows before the step's first token come from `tail` fp32 [taps - 1, E] (unit-RMS rows xh, oldest first; zeros
  * at a sequence's start), which afterwards holds the step's last taps - 1 rows.  conv_w_s fp32 [E, taps], the last
- * tap meets the current token.  out_s [T, E] in act_dtype.  xhat fp32 [T, E] is scratch (needed when T > 1).
+ * tap meets the current token.  out_s [T, E] in act_dtype.  rinv fp32 [T] is scratch (needed when T > 1): the rows'
+ * 1 / sqrt(mean + eps), handed from the launch that sums to the launch that convolves.
  */
 #define CC_PAR_MAX_OUT 4
 typedef struct CcSeqParNorm {
@@ -479,7 +480,9 @@ typedef struct CcSeqParNorm {
     const float* a;  int64_t lda;
     const float* b;  int64_t ldb;
     const float* add;
-    float* xhat;
+    float* rinv;
+    float* x_out;              /* one token only (T == 1), may be NULL: the summed row goes here instead of x (a buffer of
+                                * its own), and the row's channels are spread over the GPU */
     float* tail;
     const float* gain[CC_PAR_MAX_OUT];
     const float* conv_w[CC_PAR_MAX_OUT];

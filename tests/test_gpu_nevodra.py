@@ -58,9 +58,14 @@ def test_sum_norms_and_input_convolution_carry_their_tail_across_portions(E, tap
             x = x0[at:at + m].to(DEV).contiguous()
             wd = wide[at:at + m].to(DEV).contiguous()
             outs = [torch.empty(m, E, device=DEV) for _ in range(n)]
+            spread = m == 1 and at % 2 == 1                 # one token: also the launch that spreads the row over the GPU
+            x_out = torch.empty_like(x) if spread else None
             ops.par_norm(x, [(gains[s].to(DEV), convs[s].to(DEV), outs[s]) for s in range(n)], eps, a=wd[:, 1:1 + E],
                          b=wd[:, 2 + E:2 + 2 * E], add=add.to(DEV), tail=tail if taps > 1 else None, taps=taps,
-                         xhat=torch.empty(m, E, device=DEV) if m > 1 else None)
+                         rinv=torch.empty(m, device=DEV) if m > 1 else None, x_out=x_out)
+            if spread:
+                assert torch.equal(x.cpu(), x0[at:at + m])  # the input row is left as it was
+                x = x_out
             _close(x, xs[at:at + m], 1e-6)                  # the stream after the sum
             for s in range(n):
                 _close(outs[s], want[s][at:at + m], 3e-5)
@@ -74,7 +79,7 @@ def test_norms_without_a_convolution_table_or_a_pending_sum():
     g = torch.Generator().manual_seed(2)
     x0, gain = torch.randn(5, 70, generator=g), torch.randn(70, generator=g)
     x, out = x0.to(DEV), torch.empty(5, 70, device=DEV, dtype=torch.bfloat16)
-    ops.par_norm(x, [(gain.to(DEV), None, out)], 1e-6, taps=1, xhat=torch.empty(5, 70, device=DEV))
+    ops.par_norm(x, [(gain.to(DEV), None, out)], 1e-6, taps=1, rinv=torch.empty(5, device=DEV))
     assert torch.equal(x.cpu(), x0)
     _close(out.float(), R.rms_norm(x0.double(), gain.double(), 1e-6), 1e-2)
 
