@@ -8,8 +8,6 @@ dict.
 """
 from __future__ import annotations
 
-import math
-
 import torch
 
 
@@ -55,10 +53,6 @@ def window_mask(T, size, keep_first):
     i = torch.arange(T)[:, None]
     j = torch.arange(T)[None, :]
     return (j <= i) & ((i - j < size) | (j < keep_first))
-
-
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
 
 
 def silu(z):

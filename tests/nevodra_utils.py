@@ -55,7 +55,8 @@ DEFAULT_LOOP = (1, 3, 3)     # layers 1 and 2 run three times in a row
 
 def random_weights(cfg, seed=0, decisive=False):
     """bf16 tensors under the checkpoint's names; gains and coefficients away from their neutral values.  `decisive`
-    spaces the routers' corrections further apart than the scores can vary, so that no choice is a close call: with
+    spaces the routers' corrections further apart than the scores can vary, so that no choice (of an expert or of a
+    group) is a close call: with
     random corrections a few tokens sit where two choice scores differ by less than the bf16 error of the router's
     input, either choice is a correct bf16 result, and the tokens after such a one see it too.  The bf16 runs of the
     model use decisive weights and are held to a bar for every position; the fp32 runs route by the scores."""
@@ -99,7 +100,11 @@ def random_weights(cfg, seed=0, decisive=False):
         else:
             n, F = mlp["router"]["experts"], mlp["expert"]["ff"]
             W[q + "router"] = rnd(n, E, s=E ** -0.5 * 2.0)
-            W[q + "correction"] = (torch.randperm(n, generator=g) * 1.5 - 2.0).to(torch.bfloat16) if decisive else rnd(n, s=0.3)
+            if decisive:      # 1.5 * 2^k in a random order: single choices and sums of a group's two best are all 1.5 or more apart
+                perm = torch.randperm(n, generator=g).double()
+                W[q + "correction"] = (1.5 * torch.pow(2.0, perm) if n <= 16 else 1.5 * perm).to(torch.bfloat16)
+            else:
+                W[q + "correction"] = rnd(n, s=0.3)
             names = [f"e{e}." for e in range(n)] + (["shared."] if mlp.get("shared") else [])
             for name in names:
                 Fe = mlp["shared"]["ff"] if name == "shared." else F
